@@ -1,0 +1,112 @@
+/*
+ * moe_bench_b200 -- C ABI of the B200 (sm_100a) MoE layer forward.
+ *
+ * The library is the native side of a moe_bench `MoEImplementation`
+ * (reference baseline.py:24-44) / `DistributedScheme` (reference
+ * schemes.py:40-61): the plugin's `run()` passes the tensors of a `MoEProblem`
+ * (reference data.py:24-61) as raw device pointers.  moe_bench itself has no
+ * native boundary for this path (its baseline calls vLLM's Python
+ * `fused_experts`, baseline.py:67-76; its experimental kernels are a pybind11
+ * module, kernels/tk/tk_moe.cu:1521-1540), so each entry point below cites the
+ * reference code whose work it performs.
+ *
+ * Conventions
+ *  - every pointer is a device pointer on the current CUDA device unless said
+ *    otherwise; `stream` is a cudaStream_t passed as void*;
+ *  - functions return 0 on success, a positive code on error
+ *    (1 invalid argument, 2 CUDA error, 3 driver entry point missing,
+ *    4 workspace too small, 5 unsupported shape); `mb200_last_error()` gives
+ *    the message of the calling thread's last failure;
+ *  - entry points only enqueue work on `stream`: no allocation, no
+ *    synchronisation, no host reads of device memory (except
+ *    `mb200_read_status`), so they may be called under stream capture;
+ *  - kernels never spin without a limit: a wait that expires stores
+ *    100 + <wait site> in the workspace status word and the kernel returns.
+ */
+#ifndef MOE_BENCH_B200_H_
+#define MOE_BENCH_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MB200_ABI_VERSION 1
+#define MB200_PRECISION_BF16 0
+#define MB200_PRECISION_FP8 1
+#define MB200_TILE_M 128 /* expert segments are padded to this many rows */
+
+int mb200_abi_version(void);
+const char* mb200_last_error(void);
+
+/* Router front end: softmax over `experts` logits, top-k (largest first, lowest
+ * index wins ties), weights renormalised over the selection.
+ * logits [tokens, experts] fp32 -> topk_ids [tokens, topk] int32,
+ * topk_weights [tokens, topk] fp32.  The reference has no router: it draws ids
+ * and weights directly (data.py:178-235). */
+int mb200_route_topk(const float* logits, int tokens, int experts, int topk, int32_t* topk_ids,
+                     float* topk_weights, void* stream);
+
+/* Rows the sorted/padded assignment list can need: tokens*topk plus up to 127
+ * padding rows per expert that can be hit, rounded up to MB200_TILE_M. */
+int64_t mb200_row_capacity(int64_t tokens, int topk, int local_experts);
+int64_t mb200_align_scratch_bytes(int64_t tokens, int topk, int local_experts);
+
+/* Sort-and-pad of token->expert assignments (the moe_align_block_size step of
+ * fused_experts, baseline.py:67; slot order of tk_scheme.py:98-126).
+ * topk_ids [tokens, topk] int32 global ids; expert_map [global experts] int32
+ * (global id -> local slot or -1) or NULL when every expert is local.
+ * counts [E], mtile_prefix [E+1] (cumulative 128-row tiles; padded row offset of
+ * expert e is 128*mtile_prefix[e]), sorted_ids [row_capacity] (flat assignment
+ * index token*topk+kpos per row, -1 for padding), inverse [tokens*topk] (row of
+ * each assignment, -1 if its expert is not local). */
+int mb200_align(const int32_t* topk_ids, int64_t tokens, int topk, const int32_t* expert_map,
+                int local_experts, int32_t* counts, int32_t* mtile_prefix, int32_t* sorted_ids,
+                int32_t* inverse, int64_t row_capacity, void* scratch, void* stream);
+
+/* Dynamic activation quantisation, one fp32 scale per row per 128 elements
+ * (reference.py:143-145 -> vLLM per_token_group_quant_fp8).
+ * x [rows, hidden] bf16 -> q [rows, hidden] e4m3, scales [rows, hidden/128]. */
+int mb200_group_quant_fp8(const void* x, int64_t rows, int hidden, void* q, float* scales,
+                          void* stream);
+
+/* One grouped GEMM stage on an existing schedule (stage-level checks; the
+ * forward entry points run both).  mode 0: act[row, 0:N] =
+ * SiLU(a.w1[e,0:N]) * (a.w1[e,N:2N]) for a [row_capacity, hidden] bf16 holding
+ * the sorted rows, w1 [E, 2N, hidden], act [row_capacity, N] (reference.py:113-114).
+ * mode 1: y[n, 0:hidden] = row_scale[n] * (a.w2[e]) for a [row_capacity, N],
+ * w2 [E, hidden, N], y [tokens*topk, hidden] indexed by the flat assignment n
+ * (reference.py:115,180-181).  status: one int32 in device memory, zeroed by
+ * the caller. */
+int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_capacity, const void* w,
+                            int local_experts, int hidden, int intermediate, const int32_t* counts,
+                            const int32_t* mtile_prefix, const int32_t* sorted_ids,
+                            const float* row_scale, void* out, int32_t* status, int device,
+                            void* stream);
+
+/* Bytes of caller-provided workspace for one forward of the given shape. */
+int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
+                              int local_experts, int topk);
+
+/* The layer forward, bf16 (reference.py:98-116 + 170-182; baseline.py:62-76):
+ * out[t, :] = sum_j topk_weights[t, j] * ( SiLU(x_t.w1g[e]) * (x_t.w1u[e]) ) . w2[e],
+ * e = expert_map[topk_ids[t, j]], skipping experts that are not local.
+ * hidden_states [tokens, hidden] bf16; w1 [E_local, 2*intermediate, hidden]
+ * (gate rows, then up rows); w2 [E_local, hidden, intermediate]; out
+ * [tokens, hidden] bf16.  The workspace may be reused by the next call on the
+ * same stream; calls that overlap on the device need separate workspaces. */
+int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void* w2,
+                           const int32_t* topk_ids, const float* topk_weights,
+                           const int32_t* expert_map, void* out, int64_t tokens, int hidden,
+                           int intermediate, int local_experts, int topk, void* workspace,
+                           int64_t workspace_bytes, int device, void* stream);
+
+/* Copies the workspace status word to the host after synchronising `stream`
+ * (0 = no kernel gave up a wait).  Not capturable. */
+int mb200_read_status(const void* workspace, int32_t* status_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_BENCH_B200_H_ */

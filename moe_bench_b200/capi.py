@@ -1,0 +1,174 @@
+"""ctypes binding of ``libmoe_bench_b200.so`` (declared in ``include/moe_bench_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, an exception is
+raised.  Tensors are passed as raw device pointers and the current torch stream
+is used, so calls are ordered with surrounding torch work.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libmoe_bench_b200.so")
+
+PRECISION_BF16 = 0
+PRECISION_FP8 = 1
+TILE_M = 128
+
+c_i32, c_i64, c_vp = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
+
+# name -> (restype, argtypes); must list every symbol the header declares.
+SIGNATURES = {
+    "mb200_abi_version": (c_i32, []),
+    "mb200_last_error": (ctypes.c_char_p, []),
+    "mb200_route_topk": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp]),
+    "mb200_row_capacity": (c_i64, [c_i64, c_i32, c_i32]),
+    "mb200_align_scratch_bytes": (c_i64, [c_i64, c_i32, c_i32]),
+    "mb200_align": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
+    "mb200_group_quant_fp8": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
+    "mb200_grouped_gemm_bf16": (
+        c_i32,
+        [c_i32, c_vp, c_i64, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp],
+    ),
+    "mb200_workspace_bytes": (c_i64, [c_i32, c_i64, c_i32, c_i32, c_i32, c_i32]),
+    "mb200_moe_forward_bf16": (
+        c_i32,
+        [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64, c_i32, c_vp],
+    ),
+    "mb200_read_status": (c_i32, [c_vp, c_vp, c_vp]),
+}
+
+
+class MB200Error(RuntimeError):
+    """A library call returned a non-zero status."""
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once) and set the prototypes."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise MB200Error(
+                f"{LIB_PATH} is missing: build it with `python -m moe_bench_b200.build` "
+                "(there is no non-CUDA fallback)"
+            )
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise MB200Error(f"{what} failed (status {rc}): {load().mb200_last_error().decode()}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _need(t: torch.Tensor, dtype, name: str) -> None:
+    if not t.is_cuda or not t.is_contiguous() or t.dtype != dtype:
+        raise MB200Error(f"{name}: need a contiguous CUDA tensor of {dtype}, got {t.dtype} on {t.device}")
+
+
+def row_capacity(tokens: int, topk: int, local_experts: int) -> int:
+    return int(load().mb200_row_capacity(tokens, topk, local_experts))
+
+
+def workspace_bytes(precision: int, tokens: int, hidden: int, intermediate: int, local_experts: int, topk: int) -> int:
+    n = int(load().mb200_workspace_bytes(precision, tokens, hidden, intermediate, local_experts, topk))
+    if n < 0:
+        raise MB200Error(f"workspace_bytes: {load().mb200_last_error().decode()}")
+    return n
+
+
+def route_topk(logits: torch.Tensor, topk: int):
+    """softmax -> top-k -> renormalise on the GPU; returns (ids int32, weights fp32)."""
+    _need(logits, torch.float32, "logits")
+    t, e = logits.shape
+    ids = torch.empty(t, topk, dtype=torch.int32, device=logits.device)
+    w = torch.empty(t, topk, dtype=torch.float32, device=logits.device)
+    _check(load().mb200_route_topk(_ptr(logits), t, e, topk, _ptr(ids), _ptr(w), _stream(logits.device)), "route_topk")
+    return ids, w
+
+
+def align(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], local_experts: int):
+    """Sort-and-pad; returns (counts[E], mtile_prefix[E+1], sorted_ids[cap], inverse[T*k])."""
+    _need(topk_ids, torch.int32, "topk_ids")
+    if expert_map is not None:
+        _need(expert_map, torch.int32, "expert_map")
+    t, k = topk_ids.shape
+    dev = topk_ids.device
+    cap = row_capacity(t, k, local_experts)
+    counts = torch.empty(local_experts, dtype=torch.int32, device=dev)
+    prefix = torch.empty(local_experts + 1, dtype=torch.int32, device=dev)
+    sorted_ids = torch.full((cap,), -2, dtype=torch.int32, device=dev)
+    inverse = torch.empty(max(t * k, 1), dtype=torch.int32, device=dev)
+    scratch = torch.empty(load().mb200_align_scratch_bytes(t, k, local_experts), dtype=torch.uint8, device=dev)
+    _check(
+        load().mb200_align(
+            _ptr(topk_ids), t, k, _ptr(expert_map), local_experts, _ptr(counts), _ptr(prefix),
+            _ptr(sorted_ids), _ptr(inverse), cap, _ptr(scratch), _stream(dev),
+        ),
+        "align",
+    )
+    return counts, prefix, sorted_ids, inverse[: t * k]
+
+
+def group_quant_fp8(x: torch.Tensor):
+    """Per-row, per-128 e4m3 quantisation; returns (q e4m3 [m,K], scales fp32 [m,K/128])."""
+    _need(x, torch.bfloat16, "x")
+    m, k = x.shape
+    q = torch.empty(m, k, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(m, k // 128, dtype=torch.float32, device=x.device)
+    _check(load().mb200_group_quant_fp8(_ptr(x), m, k, _ptr(q), _ptr(s), _stream(x.device)), "group_quant_fp8")
+    return q, s
+
+
+def grouped_gemm_bf16(mode, a, w, hidden, intermediate, counts, prefix, sorted_ids, row_scale, out, status):
+    """One grouped GEMM stage (mode 0 gate/up + SiLU-mul, mode 1 down + weight)."""
+    dev = a.device
+    _check(
+        load().mb200_grouped_gemm_bf16(
+            mode, _ptr(a), a.shape[0], _ptr(w), w.shape[0], hidden, intermediate, _ptr(counts),
+            _ptr(prefix), _ptr(sorted_ids), _ptr(row_scale), _ptr(out), _ptr(status), dev.index or 0, _stream(dev),
+        ),
+        "grouped_gemm_bf16",
+    )
+
+
+def moe_forward_bf16(x, w1, w2, topk_ids, topk_weights, expert_map, out, workspace):
+    """Enqueue the bf16 layer forward on the current stream."""
+    t, hidden = x.shape
+    e_local, two_n, _ = w1.shape
+    dev = x.device
+    _check(
+        load().mb200_moe_forward_bf16(
+            _ptr(x), _ptr(w1), _ptr(w2), _ptr(topk_ids), _ptr(topk_weights), _ptr(expert_map), _ptr(out),
+            t, hidden, two_n // 2, e_local, topk_ids.shape[1], _ptr(workspace), workspace.numel(),
+            dev.index or 0, _stream(dev),
+        ),
+        "moe_forward_bf16",
+    )
+
+
+def read_status(workspace: torch.Tensor) -> int:
+    """Synchronise and return the workspace status word (0 = ok)."""
+    val = ctypes.c_int32(0)
+    _check(load().mb200_read_status(_ptr(workspace), ctypes.byref(val), _stream(workspace.device)), "read_status")
+    return int(val.value)

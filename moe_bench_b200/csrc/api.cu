@@ -1,0 +1,268 @@
+// extern "C" entry points (declared in include/moe_bench_b200.h), tensor-map
+// creation and the workspace layout of the forward.
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/moe_bench_b200.h"
+#include "layer.cuh"
+
+namespace mb200 {
+
+namespace {
+thread_local char g_last_error[512] = "";
+}
+
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+// ---------------------------------------------------------------------------
+// Tensor maps.  cuTensorMapEncodeTiled is resolved through the runtime so the
+// library carries no link-time dependency on the driver library.
+// ---------------------------------------------------------------------------
+namespace {
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+}  // namespace
+
+int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows,
+                       uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  MB200_REQUIRE(fn != nullptr, kDriverEntryMissing, "cuTensorMapEncodeTiled is not available");
+  MB200_REQUIRE(elem_bytes == 1 || elem_bytes == 2, kInvalidArgument, "tensor map: element size %d", elem_bytes);
+  MB200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, kInvalidArgument,
+                "tensor map: base address must be 16-byte aligned");
+  MB200_REQUIRE((cols * elem_bytes) % 16 == 0, kUnsupportedShape,
+                "tensor map: row pitch %llu bytes must be a multiple of 16",
+                (unsigned long long)(cols * elem_bytes));
+  MB200_REQUIRE(box_rows >= 1 && box_rows <= 256, kInvalidArgument, "tensor map: box of %u rows", box_rows);
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * elem_bytes};
+  const cuuint32_t box[2] = {uint32_t(128 / elem_bytes), box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                  2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MB200_REQUIRE(r == CUDA_SUCCESS, kCudaError, "cuTensorMapEncodeTiled failed with code %d", int(r));
+  return kOk;
+}
+
+// ---------------------------------------------------------------------------
+// Workspace layout
+// ---------------------------------------------------------------------------
+namespace {
+
+int64_t row_capacity(int64_t tokens, int topk, int local_experts) {
+  const int64_t a = tokens * topk;
+  const int64_t touched = a < local_experts ? a : local_experts;
+  const int64_t rows = a + touched * (kTileM - 1);
+  return (rows + kTileM - 1) / kTileM * kTileM;
+}
+
+struct Layout {
+  int64_t status, counts, prefix, sorted, inverse, scratch, xg, act, y, total;
+};
+
+int64_t align_up(int64_t v) { return (v + 1023) / 1024 * 1024; }
+
+Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk) {
+  (void)precision;
+  const int64_t a = tokens * topk;
+  const int64_t cap = row_capacity(tokens, topk, local_experts);
+  Layout l;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { int64_t o = off; off = align_up(off + bytes); return o; };
+  l.status = take(256);
+  l.counts = take(int64_t(local_experts) * 4);
+  l.prefix = take(int64_t(local_experts + 1) * 4);
+  l.sorted = take(cap * 4);
+  l.inverse = take((a > 0 ? a : 1) * 4);
+  l.scratch = take(align_scratch_ints(a, local_experts) * 4);
+  l.xg = take(cap * hidden * 2);
+  l.act = take(cap * intermediate * 2);
+  l.y = take((a > 0 ? a : 1) * int64_t(hidden) * 2);
+  l.total = off;
+  return l;
+}
+
+cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts, int topk) {
+  MB200_REQUIRE(tokens >= 0 && topk >= 1 && local_experts >= 1, kInvalidArgument,
+                "shape: tokens=%lld topk=%d local_experts=%d", (long long)tokens, topk, local_experts);
+  MB200_REQUIRE(local_experts <= kMaxExperts, kUnsupportedShape, "local_experts=%d > %d", local_experts, kMaxExperts);
+  MB200_REQUIRE(hidden > 0 && hidden % 64 == 0, kUnsupportedShape, "hidden=%d must be a positive multiple of 64", hidden);
+  MB200_REQUIRE(intermediate > 0 && intermediate % 64 == 0, kUnsupportedShape,
+                "intermediate=%d must be a positive multiple of 64", intermediate);
+  MB200_REQUIRE(tokens * topk < (int64_t(1) << 31) - 4096 * 128, kUnsupportedShape,
+                "tokens*topk=%lld does not fit 32-bit row indices", (long long)(tokens * topk));
+  return kOk;
+}
+
+int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
+                   int intermediate, const int* counts, const int* prefix, const int* sorted,
+                   const float* row_scale, void* out, int* status, int device, cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  GemmArgs g{};
+  g.counts = counts;
+  g.mtile_prefix = prefix;
+  g.sorted_ids = sorted;
+  g.num_experts = local_experts;
+  g.row_scale = row_scale;
+  g.out = out;
+  g.status = status;
+  int rc;
+  if (mode == kGateUpSwiglu) {
+    if ((rc = make_tensor_map_2d(&map_a, a, 2, uint64_t(cap), uint64_t(hidden), kTileM))) return rc;
+    if ((rc = make_tensor_map_2d(&map_b, w, 2, uint64_t(local_experts) * 2 * intermediate, uint64_t(hidden), 128))) return rc;
+    g.n_tiles = (intermediate + 127) / 128;
+    g.k_iters = (hidden + 63) / 64;
+    g.b_rows_per_expert = 2 * intermediate;
+    g.b_half_offset = intermediate;
+    g.out_cols = intermediate;
+  } else {
+    if ((rc = make_tensor_map_2d(&map_a, a, 2, uint64_t(cap), uint64_t(intermediate), kTileM))) return rc;
+    if ((rc = make_tensor_map_2d(&map_b, w, 2, uint64_t(local_experts) * hidden, uint64_t(intermediate), 256))) return rc;
+    g.n_tiles = (hidden + 255) / 256;
+    g.k_iters = (intermediate + 63) / 64;
+    g.b_rows_per_expert = hidden;
+    g.b_half_offset = 0;
+    g.out_cols = hidden;
+  }
+  return launch_grouped_gemm_bf16(GemmMode(mode), map_a, map_b, g, device, stream);
+}
+
+}  // namespace
+}  // namespace mb200
+
+using namespace mb200;
+
+extern "C" {
+
+int mb200_abi_version(void) { return MB200_ABI_VERSION; }
+
+const char* mb200_last_error(void) { return g_last_error; }
+
+int mb200_route_topk(const float* logits, int tokens, int experts, int topk, int32_t* topk_ids,
+                     float* topk_weights, void* stream) {
+  MB200_REQUIRE(tokens >= 0, kInvalidArgument, "route_topk: tokens=%d", tokens);
+  MB200_REQUIRE(tokens == 0 || (logits && topk_ids && topk_weights), kInvalidArgument, "route_topk: null pointer");
+  return launch_route_topk(logits, tokens, experts, topk, topk_ids, topk_weights, as_stream(stream));
+}
+
+int64_t mb200_row_capacity(int64_t tokens, int topk, int local_experts) {
+  return row_capacity(tokens, topk, local_experts);
+}
+
+int64_t mb200_align_scratch_bytes(int64_t tokens, int topk, int local_experts) {
+  return align_scratch_ints(tokens * topk, local_experts) * 4;
+}
+
+int mb200_align(const int32_t* topk_ids, int64_t tokens, int topk, const int32_t* expert_map,
+                int local_experts, int32_t* counts, int32_t* mtile_prefix, int32_t* sorted_ids,
+                int32_t* inverse, int64_t row_cap, void* scratch, void* stream) {
+  MB200_REQUIRE(tokens >= 0 && topk >= 1, kInvalidArgument, "align: tokens=%lld topk=%d", (long long)tokens, topk);
+  MB200_REQUIRE(counts && mtile_prefix && sorted_ids && scratch && (tokens == 0 || (topk_ids && inverse)),
+                kInvalidArgument, "align: null pointer");
+  MB200_REQUIRE(row_cap >= row_capacity(tokens, topk, local_experts), kWorkspaceTooSmall,
+                "align: row capacity %lld < %lld", (long long)row_cap,
+                (long long)row_capacity(tokens, topk, local_experts));
+  Schedule s{counts, mtile_prefix, sorted_ids, inverse};
+  return launch_align(topk_ids, tokens * topk, expert_map, local_experts, s, row_cap,
+                      reinterpret_cast<int*>(scratch), as_stream(stream));
+}
+
+int mb200_group_quant_fp8(const void* x, int64_t rows, int hidden, void* q, float* scales, void* stream) {
+  MB200_REQUIRE(rows >= 0 && (rows == 0 || (x && q && scales)), kInvalidArgument, "group_quant: bad argument");
+  return launch_group_quant_fp8(reinterpret_cast<const __nv_bfloat16*>(x), rows, hidden,
+                                reinterpret_cast<uint8_t*>(q), scales, hidden / 128, 0, as_stream(stream));
+}
+
+int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_cap, const void* w, int local_experts,
+                            int hidden, int intermediate, const int32_t* counts,
+                            const int32_t* mtile_prefix, const int32_t* sorted_ids,
+                            const float* row_scale, void* out, int32_t* status, int device, void* stream) {
+  MB200_REQUIRE(mode == 0 || mode == 1, kInvalidArgument, "grouped_gemm: mode=%d", mode);
+  MB200_REQUIRE(a && w && counts && mtile_prefix && sorted_ids && out && (mode == 0 || row_scale),
+                kInvalidArgument, "grouped_gemm: null pointer");
+  MB200_REQUIRE(row_cap > 0 && row_cap % kTileM == 0, kInvalidArgument,
+                "grouped_gemm: row capacity %lld must be a positive multiple of %d", (long long)row_cap, kTileM);
+  int rc = check_shape(0, hidden, intermediate, local_experts, 1);
+  if (rc) return rc;
+  return run_gemm_stage(mode, a, row_cap, w, local_experts, hidden, intermediate, counts, mtile_prefix,
+                        sorted_ids, row_scale, out, status, device, as_stream(stream));
+}
+
+int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
+                              int local_experts, int topk) {
+  if (check_shape(tokens, hidden, intermediate, local_experts, topk)) return -1;
+  if (precision != MB200_PRECISION_BF16) {
+    set_last_error("workspace_bytes: precision %d is not built", precision);
+    return -1;
+  }
+  return make_layout(precision, tokens, hidden, intermediate, local_experts, topk).total;
+}
+
+int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void* w2,
+                           const int32_t* topk_ids, const float* topk_weights,
+                           const int32_t* expert_map, void* out, int64_t tokens, int hidden,
+                           int intermediate, int local_experts, int topk, void* workspace,
+                           int64_t workspace_bytes, int device, void* stream) {
+  int rc = check_shape(tokens, hidden, intermediate, local_experts, topk);
+  if (rc) return rc;
+  if (tokens == 0) return kOk;
+  MB200_REQUIRE(hidden_states && w1 && w2 && topk_ids && topk_weights && out && workspace, kInvalidArgument,
+                "moe_forward_bf16: null pointer");
+  const Layout l = make_layout(MB200_PRECISION_BF16, tokens, hidden, intermediate, local_experts, topk);
+  MB200_REQUIRE(workspace_bytes >= l.total, kWorkspaceTooSmall, "moe_forward_bf16: workspace %lld < %lld bytes",
+                (long long)workspace_bytes, (long long)l.total);
+  MB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, kInvalidArgument,
+                "moe_forward_bf16: workspace must be 1024-byte aligned");
+  cudaStream_t s = as_stream(stream);
+  char* ws = reinterpret_cast<char*>(workspace);
+  int* status = reinterpret_cast<int*>(ws + l.status);
+  Schedule sched{reinterpret_cast<int*>(ws + l.counts), reinterpret_cast<int*>(ws + l.prefix),
+                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse)};
+  const int64_t cap = row_capacity(tokens, topk, local_experts);
+  __nv_bfloat16* xg = reinterpret_cast<__nv_bfloat16*>(ws + l.xg);
+  __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(ws + l.act);
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);
+
+  if ((rc = launch_align(topk_ids, tokens * topk, expert_map, local_experts, sched, cap,
+                         reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
+  if ((rc = launch_gather_rows_bf16(reinterpret_cast<const __nv_bfloat16*>(hidden_states), sched, local_experts,
+                                    topk, hidden, xg, cap, s))) return rc;
+  if ((rc = run_gemm_stage(kGateUpSwiglu, xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
+                           sched.mtile_prefix, sched.sorted_ids, nullptr, act, status, device, s))) return rc;
+  if ((rc = run_gemm_stage(kDownWeighted, act, cap, w2, local_experts, hidden, intermediate, sched.counts,
+                           sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s))) return rc;
+  return launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
+}
+
+int mb200_read_status(const void* workspace, int32_t* status_out, void* stream) {
+  MB200_REQUIRE(workspace && status_out, kInvalidArgument, "read_status: null pointer");
+  MB200_CHECK_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  MB200_CHECK_CUDA(cudaMemcpy(status_out, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  return kOk;
+}
+
+}  // extern "C"

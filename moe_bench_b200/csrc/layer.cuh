@@ -1,0 +1,65 @@
+// Internal interfaces between the translation units of the library: the
+// schedule produced by the sort-and-pad step, kernel launchers, and the
+// workspace layout used by the forward entry points.
+#pragma once
+
+#include "common.cuh"
+
+namespace mb200 {
+
+constexpr int kTileM = 128;        // rows per M tile; expert segments are padded to it
+constexpr int kMaxExperts = 1024;  // local experts per rank supported by the kernels
+
+// Output of the sort-and-pad step, all in device memory.
+struct Schedule {
+  int* counts;        // [E]    real rows per local expert
+  int* mtile_prefix;  // [E+1]  cumulative M tiles; padded row offset = 128 * prefix
+  int* sorted_ids;    // [P]    flat assignment index (token*k + kpos) per row, -1 = padding
+  int* inverse;       // [A]    row of each assignment, -1 = expert not on this rank
+};
+
+// ---- route_align.cu ---------------------------------------------------------------
+int launch_route_topk(const float* logits, int tokens, int experts, int topk, int* ids,
+                      float* weights, cudaStream_t stream);
+// scratch: int[align_scratch_ints(A, E)]
+int64_t align_scratch_ints(int64_t assignments, int experts);
+int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map,
+                 int local_experts, Schedule sched, int64_t row_capacity, int* scratch,
+                 cudaStream_t stream);
+
+// ---- rows.cu ------------------------------------------------------------------------
+int launch_gather_rows_bf16(const __nv_bfloat16* x, const Schedule& sched, int local_experts,
+                            int topk, int hidden, __nv_bfloat16* xg, int64_t row_capacity,
+                            cudaStream_t stream);
+int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, int topk,
+                        int hidden, __nv_bfloat16* out, cudaStream_t stream);
+// Per-row, per-128-group e4m3 quantisation.  scales_t is [K/128][scale_ld] (group-major).
+int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uint8_t* q,
+                           float* scales, int64_t scale_ld, int transposed, cudaStream_t stream);
+
+// ---- grouped_gemm.cu -----------------------------------------------------------------
+struct GemmArgs {
+  const int* counts;
+  const int* mtile_prefix;
+  const int* sorted_ids;
+  int num_experts;
+  int n_tiles;            // output tiles per expert along the B rows
+  int k_iters;            // 128-byte K slices per tile
+  int b_rows_per_expert;  // rows of the 2-D weight view per expert
+  int b_half_offset;      // gate/up: row offset of the up half inside one expert
+  int out_cols;           // row length of the output
+  void* out;
+  const float* row_scale;  // per-assignment combine weight (second GEMM)
+  int* status;
+};
+enum GemmMode : int { kGateUpSwiglu = 0, kDownWeighted = 1 };
+int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                             const GemmArgs& args, int device, cudaStream_t stream);
+
+// ---- tensormap.cu ----------------------------------------------------------------------
+// Row-major 2-D tensor [rows][cols] of elem_bytes elements, boxes of
+// box_rows x (128 bytes of columns), 128-byte swizzle.
+int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows,
+                       uint64_t cols, uint32_t box_rows);
+
+}  // namespace mb200

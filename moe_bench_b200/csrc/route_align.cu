@@ -1,0 +1,339 @@
+// Routing front end and the sort-and-pad ("moe_align") step.
+//
+//  * route_topk: softmax over the expert logits, top-k selection, weights
+//    renormalised over the selected experts.  One warp per token; the selection
+//    is k rounds of a warp-shuffle arg-max (largest logit first, lowest expert
+//    index wins ties).  The reference has no router (data.py:178-235 draws the
+//    ids directly); this is the front end a caller with logits needs.
+//
+//  * align: stable counting sort of the flat assignment index n = token*k+kpos
+//    by local expert slot, every expert segment padded to 128 rows.  It
+//    reproduces the slot order of the reference's schedule builder on one rank
+//    (tk_scheme.py:98-126, equal to the argsort key of tk_scheme.py:338-342)
+//    and replaces the moe_align_block_size step inside fused_experts
+//    (baseline.py:67).  Work is cut into contiguous "units" of assignments, one
+//    warp each: per-unit warp-shuffle histograms (match.any), an exclusive scan
+//    over units and experts, then a scatter that replays the same match.any
+//    ranks, so the order inside an expert is ascending n whatever the grid.
+
+#include "layer.cuh"
+
+namespace mb200 {
+
+namespace {
+
+// ---------------------------------------------------------------- route_topk
+constexpr int kRouteMaxPerLane = 32;  // experts <= 1024
+
+__global__ void route_topk_kernel(const float* __restrict__ logits, int tokens, int experts,
+                                  int topk, int* __restrict__ ids, float* __restrict__ weights) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int token = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (token >= tokens) return;
+  const float* row = logits + size_t(token) * experts;
+
+  // lane l holds experts l, l+32, ... (coalesced loads)
+  float v[kRouteMaxPerLane];
+  const int per_lane = (experts + 31) >> 5;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    if (i < per_lane) {
+      int e = i * 32 + lane;
+      v[i] = e < experts ? row[e] : -INFINITY;
+      mx = fmaxf(mx, v[i]);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+
+  float sel_sum = 0.f;
+  float my_w = 0.f;   // lane j keeps the j-th selected expert's exp(logit - max)
+  int my_id = 0;
+  for (int j = 0; j < topk; ++j) {
+    // local arg-max (lowest index first on ties: i ascending, strict >)
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+      if (i < per_lane) {
+        int e = i * 32 + lane;
+        if (e < experts && (v[i] > best || (v[i] == best && e < best_e))) { best = v[i]; best_e = e; }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    // retire the winner
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kRouteMaxPerLane; ++i)
+        if (i == (best_e >> 5)) v[i] = -INFINITY;
+    }
+    float p = expf(best - mx);
+    sel_sum += p;
+    if (lane == (j & 31)) { my_w = p; my_id = best_e; }
+    if ((j & 31) == 31 || j == topk - 1) {
+      // flush up to 32 selections; the renormalisation needs the final sum, so
+      // weights are written unnormalised here and scaled below when topk > 32
+      int base = j & ~31;
+      if (base + lane <= j) {
+        ids[size_t(token) * topk + base + lane] = my_id;
+        weights[size_t(token) * topk + base + lane] = my_w;
+      }
+    }
+  }
+  __syncwarp();
+  const float inv = 1.0f / sel_sum;
+  for (int j = lane; j < topk; j += 32) weights[size_t(token) * topk + j] *= inv;
+}
+
+// ---------------------------------------------------------------- align
+constexpr int kAlignWarps = 8;
+constexpr int kAlignThreads = kAlignWarps * 32;
+constexpr int kMaxUnits = 1024;
+constexpr int kFusedMaxAssignments = 16384;
+constexpr int kFusedWarps = 32;
+
+__host__ __device__ inline int64_t unit_chunk(int64_t assignments, int units_cap) {
+  int64_t chunk = (assignments + units_cap - 1) / units_cap;
+  chunk = (chunk + 31) / 32 * 32;
+  return chunk < 1024 ? 1024 : chunk;
+}
+
+__device__ __forceinline__ int slot_of(const int* topk_ids, const int* expert_map, int64_t n,
+                                       int64_t assignments, int local_experts) {
+  if (n >= assignments) return -1;
+  int e = __ldg(topk_ids + n);
+  if (expert_map) e = (e >= 0) ? __ldg(expert_map + e) : -1;
+  return (e >= 0 && e < local_experts) ? e : -1;
+}
+
+// Walk one unit in order, 32 assignments at a time.  `running[e]` counts the
+// unit's assignments to expert e seen so far.  Emit(n, slot, rank) gets the rank
+// of assignment n among the unit's assignments to the same expert.
+template <class Emit>
+__device__ __forceinline__ void walk_unit(const int* topk_ids, const int* expert_map,
+                                          int64_t begin, int64_t end, int64_t assignments,
+                                          int local_experts, int* running, Emit emit) {
+  const int lane = threadIdx.x & 31;
+  for (int64_t base = begin; base < end; base += 32) {
+    const int64_t n = base + lane;
+    const int slot = (n < end) ? slot_of(topk_ids, expert_map, n, assignments, local_experts) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, slot);
+    if (slot >= 0) {
+      const int before = __popc(peers & ((1u << lane) - 1u));
+      const int seen = running[slot];
+      emit(n, slot, seen + before);
+    } else if (n < assignments && n < end) {
+      emit(n, -1, 0);
+    }
+    __syncwarp();
+    if (slot >= 0 && (peers & ((1u << lane) - 1u)) == 0) running[slot] += __popc(peers);
+    __syncwarp();
+  }
+}
+
+__global__ void align_count_kernel(const int* __restrict__ topk_ids, const int* __restrict__ expert_map,
+                                   int64_t assignments, int local_experts, int64_t chunk, int units,
+                                   int* __restrict__ unit_hist) {
+  extern __shared__ int hist_smem[];
+  const int warp = threadIdx.x >> 5;
+  const int unit = blockIdx.x * kAlignWarps + warp;
+  int* running = hist_smem + warp * local_experts;
+  for (int e = threadIdx.x & 31; e < local_experts; e += 32) running[e] = 0;
+  __syncwarp();
+  if (unit >= units) return;
+  const int64_t begin = int64_t(unit) * chunk;
+  const int64_t end = begin + chunk < assignments ? begin + chunk : assignments;
+  walk_unit(topk_ids, expert_map, begin, end, assignments, local_experts, running,
+            [](int64_t, int, int) {});
+  for (int e = threadIdx.x & 31; e < local_experts; e += 32)
+    unit_hist[size_t(unit) * local_experts + e] = running[e];
+}
+
+// One block.  unit_hist[u][e] becomes the exclusive prefix over units; counts and
+// the cumulative M-tile table are written.
+__device__ void scan_units_and_experts(int* unit_hist, int units, int local_experts, int* counts,
+                                       int* mtile_prefix, int* smem_tiles /*[E+1]*/) {
+  for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
+    int run = 0;
+    for (int u0 = 0; u0 < units; u0 += 8) {
+      int v[8];  // loads first, so eight of them are in flight together
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = (u0 + i < units) ? unit_hist[size_t(u0 + i) * local_experts + e] : 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (u0 + i < units) unit_hist[size_t(u0 + i) * local_experts + e] = run;
+        run += v[i];
+      }
+    }
+    counts[e] = run;
+    smem_tiles[e] = (run + kTileM - 1) / kTileM;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // warp scan: each lane owns a contiguous run of experts
+    const int lane = threadIdx.x;
+    const int per = (local_experts + 31) / 32;
+    const int lo = lane * per;
+    const int hi = lo + per < local_experts ? lo + per : local_experts;
+    int sum = 0;
+    for (int e = lo; e < hi; ++e) sum += smem_tiles[e];
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    int run = incl - sum;
+    for (int e = lo; e < hi; ++e) {
+      int t = smem_tiles[e];
+      mtile_prefix[e] = run;
+      run += t;
+    }
+    if (lane == 31) mtile_prefix[local_experts] = incl;
+  }
+}
+
+__global__ void align_scan_kernel(int* unit_hist, int units, int local_experts, int* counts,
+                                  int* mtile_prefix) {
+  extern __shared__ int tiles_smem[];
+  scan_units_and_experts(unit_hist, units, local_experts, counts, mtile_prefix, tiles_smem);
+}
+
+__device__ __forceinline__ void fill_padding(const int* counts, const int* mtile_prefix, int e,
+                                             int* sorted_ids, int64_t row_capacity) {
+  const int64_t begin = int64_t(mtile_prefix[e]) * kTileM + counts[e];
+  int64_t end = int64_t(mtile_prefix[e + 1]) * kTileM;
+  if (end > row_capacity) end = row_capacity;
+  for (int64_t p = begin + threadIdx.x; p < end; p += blockDim.x) sorted_ids[p] = -1;
+}
+
+__global__ void align_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ expert_map,
+                                     int64_t assignments, int local_experts, int64_t chunk, int units,
+                                     const int* __restrict__ unit_base, const int* __restrict__ counts,
+                                     const int* __restrict__ mtile_prefix, int* __restrict__ sorted_ids,
+                                     int* __restrict__ inverse, int64_t row_capacity) {
+  extern __shared__ int hist_smem[];
+  for (int e = blockIdx.x; e < local_experts; e += gridDim.x)
+    fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity);
+
+  const int warp = threadIdx.x >> 5;
+  const int unit = blockIdx.x * kAlignWarps + warp;
+  int* running = hist_smem + warp * local_experts;
+  for (int e = threadIdx.x & 31; e < local_experts; e += 32) running[e] = 0;
+  __syncwarp();
+  if (unit >= units) return;
+  const int64_t begin = int64_t(unit) * chunk;
+  const int64_t end = begin + chunk < assignments ? begin + chunk : assignments;
+  const int* base = unit_base + size_t(unit) * local_experts;
+  walk_unit(topk_ids, expert_map, begin, end, assignments, local_experts, running,
+            [&](int64_t n, int slot, int rank) {
+              if (slot < 0) { inverse[n] = -1; return; }
+              const int64_t row = int64_t(mtile_prefix[slot]) * kTileM + base[slot] + rank;
+              if (row < row_capacity) sorted_ids[row] = int(n);
+              inverse[n] = int(row);
+            });
+}
+
+// Whole step in one block of 32 warps (small problems: one launch instead of three).
+__global__ void __launch_bounds__(kFusedWarps * 32)
+align_fused_kernel(const int* __restrict__ topk_ids, const int* __restrict__ expert_map,
+                   int64_t assignments, int local_experts, int* __restrict__ counts,
+                   int* __restrict__ mtile_prefix, int* __restrict__ sorted_ids,
+                   int* __restrict__ inverse, int64_t row_capacity, int* __restrict__ unit_hist) {
+  extern __shared__ int smem[];
+  int* tiles_smem = smem;                              // [E+1]
+  int* running_all = smem + (local_experts + 1);       // [32][E]
+  const int warp = threadIdx.x >> 5;
+  int64_t chunk = (assignments + kFusedWarps - 1) / kFusedWarps;
+  chunk = (chunk + 31) / 32 * 32;
+  const int64_t begin = warp * chunk < assignments ? warp * chunk : assignments;
+  const int64_t end = begin + chunk < assignments ? begin + chunk : assignments;
+  int* running = running_all + warp * local_experts;
+
+  for (int e = threadIdx.x & 31; e < local_experts; e += 32) running[e] = 0;
+  __syncwarp();
+  walk_unit(topk_ids, expert_map, begin, end, assignments, local_experts, running,
+            [](int64_t, int, int) {});
+  for (int e = threadIdx.x & 31; e < local_experts; e += 32)
+    unit_hist[size_t(warp) * local_experts + e] = running[e];
+  __syncthreads();
+  scan_units_and_experts(unit_hist, kFusedWarps, local_experts, counts, mtile_prefix, tiles_smem);
+  __syncthreads();
+  for (int e = 0; e < local_experts; ++e) fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity);
+  for (int e = threadIdx.x & 31; e < local_experts; e += 32) running[e] = 0;
+  __syncwarp();
+  const int* base = unit_hist + size_t(warp) * local_experts;
+  walk_unit(topk_ids, expert_map, begin, end, assignments, local_experts, running,
+            [&](int64_t n, int slot, int rank) {
+              if (slot < 0) { inverse[n] = -1; return; }
+              const int64_t row = int64_t(mtile_prefix[slot]) * kTileM + base[slot] + rank;
+              if (row < row_capacity) sorted_ids[row] = int(n);
+              inverse[n] = int(row);
+            });
+}
+
+}  // namespace
+
+int launch_route_topk(const float* logits, int tokens, int experts, int topk, int* ids,
+                      float* weights, cudaStream_t stream) {
+  MB200_REQUIRE(experts >= 1 && experts <= 32 * kRouteMaxPerLane, kUnsupportedShape,
+                "route_topk: %d experts, supported 1..%d", experts, 32 * kRouteMaxPerLane);
+  MB200_REQUIRE(topk >= 1 && topk <= experts, kInvalidArgument, "route_topk: topk=%d with %d experts",
+                topk, experts);
+  if (tokens == 0) return kOk;
+  const int warps = 4;
+  route_topk_kernel<<<(tokens + warps - 1) / warps, warps * 32, 0, stream>>>(logits, tokens, experts,
+                                                                              topk, ids, weights);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int64_t align_scratch_ints(int64_t assignments, int experts) {
+  int64_t units = kMaxUnits;
+  (void)assignments;
+  return units * experts;
+}
+
+int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map, int local_experts,
+                 Schedule sched, int64_t row_capacity, int* scratch, cudaStream_t stream) {
+  MB200_REQUIRE(local_experts >= 1 && local_experts <= kMaxExperts, kUnsupportedShape,
+                "align: %d local experts, supported 1..%d", local_experts, kMaxExperts);
+  MB200_REQUIRE(assignments >= 0 && assignments < (int64_t(1) << 31) - 4096, kUnsupportedShape,
+                "align: %lld assignments do not fit 32-bit row indices", (long long)assignments);
+  const size_t fused_smem = size_t(local_experts + 1 + kFusedWarps * local_experts) * sizeof(int);
+  if (assignments <= kFusedMaxAssignments && fused_smem <= 48 * 1024) {
+    align_fused_kernel<<<1, kFusedWarps * 32, fused_smem, stream>>>(
+        topk_ids, expert_map, assignments, local_experts, sched.counts, sched.mtile_prefix,
+        sched.sorted_ids, sched.inverse, row_capacity, scratch);
+    MB200_CHECK_CUDA(cudaGetLastError());
+    return kOk;
+  }
+  const int64_t chunk = unit_chunk(assignments, kMaxUnits);
+  const int units = int((assignments + chunk - 1) / chunk);
+  const int blocks = (units + kAlignWarps - 1) / kAlignWarps;
+  const size_t hist_smem = size_t(kAlignWarps) * local_experts * sizeof(int);
+  if (blocks > 0) {
+    align_count_kernel<<<blocks, kAlignThreads, hist_smem, stream>>>(
+        topk_ids, expert_map, assignments, local_experts, chunk, units, scratch);
+    MB200_CHECK_CUDA(cudaGetLastError());
+  }
+  align_scan_kernel<<<1, 1024, size_t(local_experts + 1) * sizeof(int), stream>>>(
+      scratch, units, local_experts, sched.counts, sched.mtile_prefix);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  const int sblocks = blocks > 0 ? blocks : 1;
+  align_scatter_kernel<<<sblocks, kAlignThreads, hist_smem, stream>>>(
+      topk_ids, expert_map, assignments, local_experts, chunk, units, scratch, sched.counts,
+      sched.mtile_prefix, sched.sorted_ids, sched.inverse, row_capacity);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace mb200

@@ -1,0 +1,178 @@
+// Row-wise, bandwidth-bound stages around the grouped GEMMs:
+//   gather_rows:   xg[row, :] = x[token(row), :] for the sorted assignment rows
+//                  (the reference replicates every token k times instead,
+//                  reference.py:103).
+//   combine:       out[t, :] = sum over the k local assignments of token t of
+//                  the already weighted rows y[t*k + j, :], fp32 sum, bf16 store
+//                  (reference.py:180-182).
+//   group_quant:   per row, per 128-wide group dynamic e4m3 quantisation of
+//                  activations (reference.py:143-145,157-163).
+// All three move 16 bytes per thread per access and size their grids as a
+// multiple of the SM count.
+
+#include "layer.cuh"
+
+namespace mb200 {
+
+namespace {
+
+__global__ void gather_rows_bf16_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted_ids,
+                                        const int* __restrict__ mtile_prefix, int local_experts,
+                                        int topk, int vec_per_row, uint4* __restrict__ xg,
+                                        int64_t row_capacity) {
+  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * kTileM;
+  if (rows > row_capacity) rows = row_capacity;
+  // one warp per row, rows strided over all warps of the grid
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int64_t row = int64_t(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += int64_t(gridDim.x) * warps_per_block) {
+    const int n = __ldg(sorted_ids + row);
+    if (n < 0) continue;  // padding rows are never read back
+    const uint4* src = x + int64_t(n / topk) * vec_per_row;
+    uint4* dst = xg + row * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
+  }
+}
+
+__device__ __forceinline__ void accumulate_bf16x8(const uint4& v, float (&acc)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+__global__ void combine_bf16_kernel(const uint4* __restrict__ y, const int* __restrict__ inverse,
+                                    int tokens, int topk, int vec_per_row, uint4* __restrict__ out) {
+  const int64_t total = int64_t(tokens) * vec_per_row;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t t = i / vec_per_row;
+    const int v = int(i - t * vec_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < topk; ++j) {
+      const int64_t n = t * topk + j;
+      if (__ldg(inverse + n) < 0) continue;  // expert on another rank: contributes zero
+      accumulate_bf16x8(__ldg(y + n * vec_per_row + v), acc);
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+    out[i] = o;
+  }
+}
+
+// One 128-wide group per 8 lanes (16 bf16 each).
+__global__ void group_quant_fp8_kernel(const uint4* __restrict__ x, int64_t rows, int groups_per_row,
+                                       uint2* __restrict__ q, float* __restrict__ scales,
+                                       int64_t scale_ld, int transposed) {
+  const int64_t total_groups = rows * groups_per_row;
+  const int sub = threadIdx.x & 7;
+  for (int64_t g = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3; g < total_groups;
+       g += (int64_t(gridDim.x) * blockDim.x) >> 3) {
+    // 16 elements = two 16-byte loads
+    const uint4* src = x + g * 16 + sub * 2;
+    uint4 a = __ldg(src), b = __ldg(src + 1);
+    float f[16];
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 fa = __bfloat1622float2(ha[i]), fb = __bfloat1622float2(hb[i]);
+      f[2 * i] = fa.x; f[2 * i + 1] = fa.y; f[8 + 2 * i] = fb.x; f[8 + 2 * i + 1] = fb.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    const unsigned group_mask = 0xFFu << (threadIdx.x & 24);  // the 8 lanes sharing this group
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, o));
+    amax = fmaxf(amax, 1e-10f);
+    const float scale = amax * (1.0f / 448.0f);
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t packed = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float qv = fminf(fmaxf(__fdiv_rn(f[4 * i + j], scale), -448.f), 448.f);
+        packed |= uint32_t(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+      }
+      w[i] = packed;
+    }
+    uint2* dst = q + g * 16 + sub * 2;
+    dst[0] = make_uint2(w[0], w[1]);
+    dst[1] = make_uint2(w[2], w[3]);
+    if (sub == 0) {
+      const int64_t row = g / groups_per_row;
+      const int64_t grp = g - row * groups_per_row;
+      if (transposed) scales[grp * scale_ld + row] = scale;
+      else scales[row * scale_ld + grp] = scale;
+    }
+  }
+}
+
+int grid_for(int64_t work_items, int threads, int device_sms, int waves) {
+  int64_t blocks = (work_items + threads - 1) / threads;
+  int64_t cap = int64_t(device_sms) * waves;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : int(blocks);
+}
+
+int sm_count() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      sms = 148;
+  }
+  return sms;
+}
+
+}  // namespace
+
+int launch_gather_rows_bf16(const __nv_bfloat16* x, const Schedule& sched, int local_experts,
+                            int topk, int hidden, __nv_bfloat16* xg, int64_t row_capacity,
+                            cudaStream_t stream) {
+  MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "gather_rows: hidden=%d must be a multiple of 8", hidden);
+  const int threads = 256;
+  // the row count lives on the device: size the grid for the capacity
+  const int blocks = grid_for(row_capacity * 32, threads, sm_count(), 16);
+  gather_rows_bf16_kernel<<<blocks, threads, 0, stream>>>(
+      reinterpret_cast<const uint4*>(x), sched.sorted_ids, sched.mtile_prefix, local_experts, topk,
+      hidden / 8, reinterpret_cast<uint4*>(xg), row_capacity);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, int topk, int hidden,
+                        __nv_bfloat16* out, cudaStream_t stream) {
+  MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "combine: hidden=%d must be a multiple of 8", hidden);
+  if (tokens == 0) return kOk;
+  const int threads = 256;
+  const int blocks = grid_for(int64_t(tokens) * (hidden / 8), threads, sm_count(), 16);
+  combine_bf16_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(y), inverse, tokens,
+                                                     topk, hidden / 8, reinterpret_cast<uint4*>(out));
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uint8_t* q, float* scales,
+                           int64_t scale_ld, int transposed, cudaStream_t stream) {
+  MB200_REQUIRE(hidden % 128 == 0, kUnsupportedShape, "group_quant: hidden=%d must be a multiple of 128", hidden);
+  if (rows == 0) return kOk;
+  const int threads = 256;
+  const int blocks = grid_for(rows * (hidden / 128) * 8, threads, sm_count(), 16);
+  group_quant_fp8_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(x), rows,
+                                                        hidden / 128, reinterpret_cast<uint2*>(q), scales,
+                                                        scale_ld, transposed);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace mb200

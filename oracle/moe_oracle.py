@@ -10,14 +10,14 @@ Parity status
 -------------
 * bf16 / fp16 layer (``moe_dense``): pinned against outputs of the reference
   itself, generated in a container where the reference imports
-  (``tests/golden/make_golden.py`` -> ``tests/golden/*.pt``).
+  (``tests/golden/make_golden.py`` -> ``tests/golden/golden.pt``).
 * sort-and-pad (``align``): pinned against the slot order produced by the
   reference's host schedule builder (``tk_scheme.py:98-126``) for world size 1,
   replayed by ``tests/golden/make_golden.py``.
 * fp8 layer (``moe_fp8``): the block matmul, SiLU-mul, bf16 round and combine
   follow ``reference.py:65-95,119-182`` and are pinned by running the
   reference's ``_reference_fp8`` with its activation quantiser replaced by
-  ``group_quant_fp8`` (golden file ``config1_fp8.pt``).  The activation
+  ``group_quant_fp8`` (cases ``config1_*_fp8`` of ``golden.pt``).  The activation
   quantiser itself is a call into vLLM 0.22.0 (``moe_kernel_quantize_input`` ->
   ``per_token_group_quant_fp8``), a third-party CUDA/Triton op that cannot run
   on a CPU and that no reference test pins at bit level: for it this oracle is
@@ -90,13 +90,14 @@ def align(topk_ids, expert_map, num_local_experts: int, tile_m: int = 128):
 
 
 def route_topk(logits: torch.Tensor, k: int):
-    """softmax over experts -> top-k (largest first, lowest index wins ties)
-    -> weights renormalised to sum to 1.  Returns (ids int32, weights fp32)."""
-    probs = torch.softmax(logits.float(), dim=-1)
-    # torch.topk does not promise an order among equal values; sort a stable
-    # key instead so the tie rule is explicit.
-    order = torch.sort(-probs, dim=-1, stable=True).indices[:, :k]
-    top = torch.gather(probs, 1, order)
+    """softmax over experts -> top-k -> weights renormalised to sum to 1.
+
+    Selection is by logit, largest first, lowest expert index on equal logits
+    (softmax is monotonic, so this is top-k of the probabilities with an
+    explicit tie rule).  Returns (ids int32, weights fp32)."""
+    lg = logits.float()
+    order = torch.sort(-lg, dim=-1, stable=True).indices[:, :k]
+    top = torch.gather(torch.softmax(lg, dim=-1), 1, order)
     return order.to(torch.int32), top / top.sum(dim=-1, keepdim=True)
 
 
@@ -154,7 +155,7 @@ def moe_dense(hidden_states, w1, w2, topk_ids, expert_map):
     rows of non-local assignments are zero."""
     t, k_dim = hidden_states.shape
     topk = topk_ids.shape[1]
-    x = hidden_states.float()
+    x = hidden_states.cpu().float()
     slots = torch.from_numpy(local_slots(topk_ids.cpu().numpy(), None if expert_map is None else expert_map.cpu().numpy()))
     tok = torch.arange(t).repeat_interleave(topk)
     out = torch.zeros(t * topk, k_dim, dtype=torch.float32)
@@ -162,8 +163,9 @@ def moe_dense(hidden_states, w1, w2, topk_ids, expert_map):
         sel = (slots == e).nonzero().flatten()
         if sel.numel() == 0:
             continue
-        h = x[tok[sel]] @ w1[e].float().t()
-        out[sel] = silu_and_mul(h) @ w2[e].float().t()
+        # weights may live on another device: only touched experts are copied
+        h = x[tok[sel]] @ w1[e].cpu().float().t()
+        out[sel] = silu_and_mul(h) @ w2[e].cpu().float().t()
     return out.view(t, topk, k_dim)
 
 
@@ -173,7 +175,7 @@ def moe_fp8(hidden_states, w1, w2, w1_scale, w2_scale, topk_ids, expert_map, blo
     dtype, quantise again, block matmul with w2."""
     t, k_dim = hidden_states.shape
     topk = topk_ids.shape[1]
-    xq, xs = group_quant_fp8(hidden_states, block_shape[1])
+    xq, xs = group_quant_fp8(hidden_states.cpu(), block_shape[1])
     slots = torch.from_numpy(local_slots(topk_ids.cpu().numpy(), None if expert_map is None else expert_map.cpu().numpy()))
     tok = torch.arange(t).repeat_interleave(topk)
     out = torch.zeros(t * topk, k_dim, dtype=torch.float32)
@@ -181,10 +183,10 @@ def moe_fp8(hidden_states, w1, w2, w1_scale, w2_scale, topk_ids, expert_map, blo
         sel = (slots == e).nonzero().flatten()
         if sel.numel() == 0:
             continue
-        h = block_matmul(xq[tok[sel]], w1[e], xs[tok[sel]], w1_scale[e], block_shape)
+        h = block_matmul(xq[tok[sel]], w1[e].cpu(), xs[tok[sel]], w1_scale[e].cpu(), block_shape)
         act = silu_and_mul(h).to(base_dtype)
         aq, a_s = group_quant_fp8(act, block_shape[1])
-        out[sel] = block_matmul(aq, w2[e], a_s, w2_scale[e], block_shape)
+        out[sel] = block_matmul(aq, w2[e].cpu(), a_s, w2_scale[e].cpu(), block_shape)
     return out.view(t, topk, k_dim)
 
 
@@ -201,7 +203,7 @@ def reference_moe(problem) -> torch.Tensor:
         )
     else:
         per = moe_dense(problem.hidden_states, problem.w1, problem.w2, problem.topk_ids, problem.expert_map)
-    return (per * problem.topk_weights.float().unsqueeze(-1)).sum(dim=1)
+    return (per * problem.topk_weights.cpu().float().unsqueeze(-1)).sum(dim=1)
 
 
 @dataclass

@@ -1,0 +1,188 @@
+"""GPU parity of the individual stages against the CPU oracle, through the C ABI.
+
+Integer stages (routing ids, sort-and-pad, e4m3 bytes) must be bit-exact;
+floating-point stages state their tolerance next to the check.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from moe_bench_b200 import capi
+from moe_bench_b200 import problem as P
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _routing(dist, tokens, experts, topk, seed=0, **kw):
+    cfg = P.MoEBenchConfig(
+        hidden_size=256, intermediate_size=128, num_experts=experts, topk=topk, world_size=1,
+        routing=P.RoutingConfig(distribution=P.Distribution(dist), **kw), seed=seed, device="cpu",
+    )
+    gen = torch.Generator().manual_seed(seed + 17)
+    return P._make_routing(cfg, tokens, gen)[0]
+
+
+ALIGN_CASES = [
+    # (distribution, tokens, experts, topk, ep_world)   ep_world 0 = no expert_map
+    ("uniform", 64, 8, 2, 0),
+    ("uniform", 1, 256, 8, 0),      # one token: 8 experts hit, 248 empty
+    ("uniform", 8, 256, 8, 0),
+    ("uniform", 128, 256, 8, 0),
+    ("single", 300, 256, 8, 0),     # every token on experts 0..7
+    ("skewed", 2048, 256, 8, 0),    # 16384 assignments: last size of the one-block path
+    ("uniform", 2049, 256, 8, 0),   # first size of the three-kernel path, ragged tail
+    ("uniform", 8192, 256, 8, 0),   # full-size sweep point
+    ("balanced", 777, 64, 8, 0),
+    ("uniform", 1024, 256, 8, 8),   # EP: rank 3 of 8 owns 32 experts
+    ("single", 512, 256, 8, 8),     # EP with no local assignment at all on rank 3
+    ("uniform", 5000, 1024, 4, 0),  # maximum supported expert count
+]
+
+
+@pytest.mark.parametrize("dist,tokens,experts,topk,ep", ALIGN_CASES)
+def test_align_bit_exact(dist, tokens, experts, topk, ep):
+    ids = _routing(dist, tokens, experts, topk)
+    emap, local = None, experts
+    if ep:
+        local = experts // ep
+        emap = torch.full((experts,), -1, dtype=torch.int32)
+        emap[3 * local : 4 * local] = torch.arange(local, dtype=torch.int32)
+    counts, prefix, sorted_ids, inverse = capi.align(
+        ids.to(DEV), None if emap is None else emap.to(DEV), local
+    )
+    torch.cuda.synchronize()
+    o_counts, o_off, o_sorted, o_inv = O.align(ids.numpy(), None if emap is None else emap.numpy(), local)
+    assert np.array_equal(counts.cpu().numpy(), o_counts)
+    assert np.array_equal(prefix.cpu().numpy() * 128, o_off)
+    rows = int(o_off[-1])
+    assert np.array_equal(sorted_ids.cpu().numpy()[:rows], o_sorted)
+    assert np.array_equal(inverse.cpu().numpy(), o_inv)
+    # rows past the last expert are never written
+    assert bool((sorted_ids[rows:] == -2).all())
+
+
+def test_align_is_a_permutation_at_full_size():
+    """Size-independent property at the largest sweep point: every local
+    assignment appears exactly once, inverse inverts sorted_ids, and rows are
+    grouped by expert in ascending assignment order."""
+    ids = _routing("uniform", 8192, 256, 8, seed=3)
+    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, 256)
+    s = sorted_ids.cpu().numpy()
+    inv = inverse.cpu().numpy()
+    real = s[s >= 0]
+    assert np.array_equal(np.sort(real), np.arange(8192 * 8))
+    assert np.array_equal(s[inv], np.arange(8192 * 8))
+    flat = ids.numpy().reshape(-1)
+    pre = prefix.cpu().numpy()
+    for e in (0, 17, 255):
+        seg = s[pre[e] * 128 : pre[e + 1] * 128]
+        seg = seg[seg >= 0]
+        assert np.all(flat[seg] == e) and np.all(np.diff(seg) > 0)
+
+
+@pytest.mark.parametrize("tokens,experts,topk", [(1, 8, 2), (64, 8, 2), (333, 256, 8), (8192, 256, 8), (50, 1000, 40)])
+def test_route_topk(tokens, experts, topk):
+    gen = torch.Generator().manual_seed(tokens * 7 + experts)
+    logits = torch.randn(tokens, experts, generator=gen)
+    if tokens > 1:
+        logits[1] = 0.0          # all equal: ties broken by lowest index
+        logits[0, 3] = logits[0, 5]
+    ids, w = capi.route_topk(logits.to(DEV), topk)
+    o_ids, o_w = O.route_topk(logits, topk)
+    assert torch.equal(ids.cpu(), o_ids)  # bit-exact selection and order
+    # weights: exp/sum evaluated in a different order than torch.softmax; fp32 rounding only
+    torch.testing.assert_close(w.cpu(), o_w, atol=1e-6, rtol=2e-5)
+
+
+def test_route_topk_single_distribution():
+    """Logits that make experts 0..7 win for every token reproduce the
+    'single' routing of the reference (data.py:198-206)."""
+    logits = torch.randn(100, 256, generator=torch.Generator().manual_seed(1))
+    logits[:, :8] = 10.0 - torch.arange(8).float() * 0.5
+    ids, _ = capi.route_topk(logits.to(DEV), 8)
+    assert torch.equal(ids.cpu(), torch.arange(8, dtype=torch.int32).repeat(100, 1))
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 128), (7, 256), (512, 7168), (4096, 2048)])
+def test_group_quant_fp8_bit_exact(rows, hidden):
+    gen = torch.Generator().manual_seed(rows + hidden)
+    x = (torch.randn(rows, hidden, generator=gen) * 3).to(torch.bfloat16)
+    x[0, :128] = 0                      # all-zero group
+    if rows > 2:
+        x[2, 5] = 3.0e4                 # one huge element sets the group's scale
+    q, s = capi.group_quant_fp8(x.to(DEV))
+    oq, os_ = O.group_quant_fp8(x)
+    assert torch.equal(s.cpu(), os_)
+    assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8))
+
+
+def _stage_problem(tokens, hidden, inter, experts, topk, dist="uniform", seed=0):
+    cfg = P.MoEBenchConfig(
+        hidden_size=hidden, intermediate_size=inter, num_experts=experts, topk=topk, world_size=1,
+        routing=P.RoutingConfig(distribution=P.Distribution(dist)), seed=seed, device="cpu",
+    )
+    return P.make_problem(cfg, tokens)
+
+
+@pytest.mark.parametrize(
+    "tokens,hidden,inter,experts,topk,dist",
+    [
+        (64, 256, 128, 8, 2, "uniform"),     # config 1: one tile per expert
+        (300, 512, 256, 4, 2, "uniform"),    # several M tiles per expert, ragged last tile
+        (40, 1024, 384, 16, 4, "single"),    # empty experts
+        (200, 192, 320, 8, 2, "uniform"),    # hidden/intermediate not multiples of the tile width
+    ],
+)
+def test_grouped_gemm_stages(tokens, hidden, inter, experts, topk, dist):
+    """Gate/up + SiLU-mul and down + weight stages against fp32 matmuls on the CPU."""
+    prob = _stage_problem(tokens, hidden, inter, experts, topk, dist)
+    ids = prob.topk_ids
+    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, experts)
+    cap = sorted_ids.shape[0]
+    s_cpu = sorted_ids.cpu()
+    x = prob.hidden_states
+    rows = (s_cpu >= 0).nonzero().flatten()
+    row_tok = (s_cpu[rows] // topk).long()
+    flat = ids.reshape(-1).long()
+    row_exp = flat[s_cpu[rows].long()]
+
+    xg = torch.zeros(cap, hidden, dtype=torch.bfloat16)
+    xg[rows] = x[row_tok]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    act = torch.full((cap, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    capi.grouped_gemm_bf16(0, xg.to(DEV), prob.w1.to(DEV), hidden, inter, counts, prefix, sorted_ids, None, act, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    h = torch.zeros(len(rows), 2 * inter)
+    for e in range(experts):
+        m = row_exp == e
+        if m.any():
+            h[m] = x[row_tok[m]].float() @ prob.w1[e].float().t()
+    ref_act = O.silu_and_mul(h)
+    got_act = act.cpu()[rows].float()
+    # fp32 accumulation of exact bf16 products, then one bf16 rounding: 2^-8 relative
+    torch.testing.assert_close(got_act, ref_act, atol=2e-3, rtol=8e-3)
+    # padding rows are never written
+    pad = (s_cpu < 0).nonzero().flatten()
+    assert bool(torch.isnan(act.cpu()[pad].float()).all())
+
+    # second stage consumes the rounded activations the first one produced
+    a2 = act.clone()
+    a2[pad.to(DEV)] = 0
+    w = prob.topk_weights.reshape(-1)
+    y = torch.full((tokens * topk, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+    capi.grouped_gemm_bf16(1, a2, prob.w2.to(DEV), hidden, inter, counts, prefix, sorted_ids, w.to(DEV), y, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref_y = torch.zeros(len(rows), hidden)
+    a_in = act.cpu()[rows].float()
+    for e in range(experts):
+        m = row_exp == e
+        if m.any():
+            ref_y[m] = a_in[m] @ prob.w2[e].float().t()
+    ref_y *= w[s_cpu[rows].long()].unsqueeze(-1)
+    got_y = y.cpu()[s_cpu[rows].long()].float()
+    torch.testing.assert_close(got_y, ref_y, atol=2e-3, rtol=8e-3)
