@@ -1,0 +1,366 @@
+"""Benchmark of the MoE layer forward (DeepSeek-V3.2 shape, bf16, compute-only).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl b200|reference]
+
+One step = one forward of the layer over one batch of T tokens per GPU
+(hidden 7168, intermediate 2048, 256 experts, top-8, uniform routing, seed 0;
+synthetic inputs from the package's seeded generator).  The metric is the
+harness's TFLOP/s: 6*N*K flops per computed assignment divided by the layer
+latency; ``ms_per_step`` is that latency.  Prints ONE JSON line on rank 0.
+
+* ``value``     inputs resident in HBM, device-timed with CUDA events.
+* ``e2e``       the same metric through the plugin call with the step's inputs
+                copied from pinned host memory and the output copied back, all
+                inside the timed region.
+* ``roofline``  the gate/up grouped GEMM (the dominant kernel), its duration read
+                from events recorded around it inside the timed region.
+* ``cpu_baseline`` / ``--impl reference``: the CPU oracle (a port of the
+                reference's torch forward) on a bounded sample of the workload.
+
+With N > 1 every rank holds all experts and its own token shard (no exchange on
+the data path), so scaling is weak and the value is the sum over ranks divided
+by the slowest rank's time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, EXPERTS, TOPK = 7168, 2048, 256, 8  # EXPERTS can be lowered with --experts for profiling
+METRIC, UNIT = "moe_layer_tflops", "TFLOP/s"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self._nv = None
+
+    _NAMES = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+    }
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in self._NAMES.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.01)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def _touched_experts(topk_ids) -> int:
+    import torch
+
+    return int(torch.unique(topk_ids).numel())
+
+
+def _cpu_sample_problem(tokens: int):
+    """Bounded CPU sample: the first four experts of the layer with every
+    assignment the T-token batch routes to them (the compute-only share of rank
+    0 of a 64-way expert split, as the reference defines it)."""
+    from moe_bench_b200 import problem as P
+
+    cfg = P.MoEBenchConfig(
+        hidden_size=HIDDEN, intermediate_size=INTER, num_experts=EXPERTS, topk=TOPK,
+        parallel_mode=P.ParallelMode.EP, world_size=64, precision=P.Precision.BF16,
+        routing=P.RoutingConfig(distribution=P.Distribution.UNIFORM), seed=0, device="cpu",
+    )
+    prob = P.make_problem(cfg, tokens, rank=0)
+    # weights pre-converted to fp32 once, outside the timed loop
+    prob = dataclasses.replace(prob, w1=prob.w1.float(), w2=prob.w2.float())
+    return prob
+
+
+def _time_cpu_oracle(tokens: int, steps: int, warmup: int, budget_s: float = 25.0):
+    import torch
+
+    from oracle import moe_oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    prob = _cpu_sample_problem(tokens)
+    assignments = prob.num_local_assignments
+    flops = 6.0 * INTER * HIDDEN * assignments
+    for _ in range(warmup):
+        O.reference_moe(prob)
+    times = []
+    t_begin = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        O.reference_moe(prob)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > budget_s:
+            break
+    avg = sum(times) / len(times)
+    return {
+        "value": flops / avg / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+        "sample": f"experts 0-3 of 256 with all {assignments} assignments of a {tokens}-token batch "
+                  f"(DSv3.2 dims, weights pre-converted to fp32), {len(times)} passes, {avg * 1e3:.1f} ms each",
+        "ms_per_pass": avg * 1e3, "passes": len(times),
+    }
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    res = _time_cpu_oracle(args.tokens, args.steps, min(args.warmup, 3), budget_s=120.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": res["passes"], "warmup": min(args.warmup, 3), "ms_per_step": res["ms_per_pass"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": _config_dict(args.tokens, world),
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def _config_dict(tokens: int, world: int):
+    return {
+        "workload": f"dsv32_bf16_compute_only_T{tokens}" + ("" if EXPERTS == 256 else f"_E{EXPERTS}"), "tokens_per_gpu": tokens, "hidden": HIDDEN,
+        "intermediate": INTER, "experts": EXPERTS, "topk": TOPK, "routing": "uniform", "seed": 0,
+        "parallelism": "single GPU" if world == 1 else f"{world} token-sharded replicas, all experts on every GPU",
+        "l2": "inputs larger than L2: 22.5 GB of expert weights are streamed every step",
+    }
+
+
+def run_b200(args, rank: int, local_rank: int, world: int) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from moe_bench_b200 import capi
+    from moe_bench_b200 import problem as P
+    from moe_bench_b200.plugin import get_implementation
+    from oracle import moe_oracle as O
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    tokens, steps, warmup = args.tokens, args.steps, args.warmup
+    cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS)
+    weights = P.make_weights(cfg)
+    x, ids, wts = P._gen_input(cfg, tokens, rank)  # every rank its own token shard
+    prob = P.MoEProblem(cfg, tokens, x, weights.w1, weights.w2, ids, wts, None, None)
+    impl = get_implementation("b200")
+    impl.setup(prob)
+    assignments = tokens * TOPK
+    flops_step = 6.0 * INTER * HIDDEN * assignments
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(warmup):
+        impl.run(prob)
+    # -------- device-resident timing, with per-stage events --------
+    stage_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(steps)]
+    for evs in stage_ev:
+        for ev in evs:
+            ev.record()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        start.record()
+        for i in range(steps):
+            capi.set_stage_events(stage_ev[i])
+            impl.run(prob)
+        end.record()
+        torch.cuda.synchronize()
+    capi.set_stage_events(None)
+    barrier()
+    ms_step = max_over_ranks(start.elapsed_time(end) / steps)
+    if impl.device_status() != 0:
+        raise RuntimeError(f"device status {impl.device_status()}")
+    stage_ms = [sum(evs[j].elapsed_time(evs[j + 1]) for evs in stage_ev) / steps for j in range(5)]
+
+    if args.skip_extras:
+        if rank == 0:
+            print(json.dumps({"ms_per_step": ms_step, "stage_ms": dict(zip(capi.STAGE_NAMES, stage_ms)),
+                              "config": _config_dict(tokens, world), "note": "profiling run, extras skipped"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # -------- end to end: host buffers in, host buffer out --------
+    hx, hi, hw = x.cpu().pin_memory(), ids.cpu().pin_memory(), wts.cpu().pin_memory()
+    hout = torch.empty(tokens, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    dx, di, dw = torch.empty_like(x), torch.empty_like(ids), torch.empty_like(wts)
+    prob_e2e = dataclasses.replace(prob, hidden_states=dx, topk_ids=di, topk_weights=dw)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        di.copy_(hi, non_blocking=True)
+        dw.copy_(hw, non_blocking=True)
+        out = impl.run(prob_e2e)
+        hout.copy_(out, non_blocking=True)
+
+    for _ in range(max(3, warmup // 2)):
+        e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(steps):
+        e2e_step()
+    e2.record()
+    torch.cuda.synchronize()
+    barrier()
+    ms_e2e = max_over_ranks(s2.elapsed_time(e2) / steps)
+    h2d = hx.numel() * 2 + hi.numel() * 4 + hw.numel() * 4
+    d2h = hout.numel() * 2
+
+    # -------- parity spot check (outside any timed region) --------
+    out = impl.run(prob).clone()
+    idx = torch.randperm(tokens, generator=torch.Generator().manual_seed(0))[: min(8, tokens)].to(dev)
+    sub = dataclasses.replace(prob, num_tokens=len(idx), hidden_states=x[idx].contiguous(),
+                              topk_ids=ids[idx].contiguous(), topk_weights=wts[idx].contiguous())
+    check = O.verify_output("bf16", out[idx], O.reference_moe(sub))
+
+    if world > 1:
+        ok = torch.tensor([1.0 if check.passed else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        passed = bool(ok.item() > 0)
+    else:
+        passed = check.passed
+
+    if rank == 0:
+        peaks = _peaks()
+        touched = _touched_experts(ids)
+        rows = assignments  # real rows; padding rows are neither loaded with data nor stored
+        gemm_bytes = touched * 2 * INTER * HIDDEN * 2 + rows * HIDDEN * 2 + rows * INTER * 2
+        gemm_flops = 4.0 * INTER * HIDDEN * assignments
+        gemm_ms = stage_ms[2]
+        t_hbm = gemm_bytes / (peaks["hbm_gbs"] * 1e9)
+        t_tc = gemm_flops / (peaks["bf16_tflops"] * 1e12)
+        if t_hbm >= t_tc:
+            roof = {"bound": "hbm", "achieved": gemm_bytes / (gemm_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s"}
+        else:
+            roof = {"bound": "tensor", "achieved": gemm_flops / (gemm_ms * 1e-3) / 1e12,
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s"}
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        roof.update({
+            "traffic": None, "kernel": "grouped_gemm_bf16_kernel<gate_up_swiglu>", "kernel_ms": gemm_ms,
+            "peak_source": peaks["source"] + " (burst)", "algorithmic_bytes": gemm_bytes,
+            "algorithmic_flops": gemm_flops, "t_hbm_ms": t_hbm * 1e3, "t_tensor_ms": t_tc * 1e3,
+        })
+        layer_bytes = touched * 3 * INTER * HIDDEN * 2 + 2 * tokens * HIDDEN * 2 + assignments * 8
+        layer_roof_ms = max(layer_bytes / (peaks["hbm_gbs"] * 1e9), flops_step / (peaks["bf16_tflops"] * 1e12)) * 1e3
+        kernels_per_step = 7 if assignments > 16384 else 5
+        line = {
+            "metric": METRIC, "value": flops_step * world / (ms_step * 1e-3) / 1e12, "unit": UNIT,
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": _config_dict(tokens, world),
+            "e2e": {"value": flops_step * world / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": kernels_per_step * steps,
+            "clocks": clocks.summary(),
+            "roofline": roof,
+            "stage_ms": dict(zip(capi.STAGE_NAMES, stage_ms)),
+            "layer_roofline_ms": layer_roof_ms, "layer_roofline_frac": layer_roof_ms / ms_step,
+            "latency_us": ms_step * 1e3,
+            "verify": "ok" if passed else "FAIL", "rel_err": check.rel_err,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            res = _time_cpu_oracle(tokens, 20, 2)
+            line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=8192, help="tokens per GPU")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=256, help="expert count (lower it only to size a profiler capture)")
+    ap.add_argument("--skip-extras", action="store_true", help="timed region only: no e2e, parity or CPU legs")
+    args = ap.parse_args()
+    global EXPERTS
+    EXPERTS = args.experts
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_b200(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -102,6 +102,15 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
                            int intermediate, int local_experts, int topk, void* workspace,
                            int64_t workspace_bytes, int device, void* stream);
 
+/* Per-stage timing hook for benchmarks.  After mb200_set_stage_events(ev, 6) the
+ * forward entry points called from this thread record ev[0] before the first
+ * stage and ev[1..5] after the sort-and-pad, row gather, gate/up GEMM, down GEMM
+ * and combine stages (cudaEvent_t handles created by the caller).  Call with
+ * (NULL, 0) to switch it off.  moe_bench times whole calls only
+ * (bench.py:52-101); this exists so one kernel's duration can be read inside a
+ * timed region. */
+int mb200_set_stage_events(void* const* events, int count);
+
 /* Copies the workspace status word to the host after synchronising `stream`
  * (0 = no kernel gave up a wait).  Not capturable. */
 int mb200_read_status(const void* workspace, int32_t* status_out, void* stream);

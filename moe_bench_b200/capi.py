@@ -40,6 +40,7 @@ SIGNATURES = {
         c_i32,
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64, c_i32, c_vp],
     ),
+    "mb200_set_stage_events": (c_i32, [c_vp, c_i32]),
     "mb200_read_status": (c_i32, [c_vp, c_vp, c_vp]),
 }
 
@@ -172,3 +173,17 @@ def read_status(workspace: torch.Tensor) -> int:
     val = ctypes.c_int32(0)
     _check(load().mb200_read_status(_ptr(workspace), ctypes.byref(val), _stream(workspace.device)), "read_status")
     return int(val.value)
+
+
+STAGE_NAMES = ("align", "gather_rows", "gate_up_gemm", "down_gemm", "combine")
+
+
+def set_stage_events(events) -> None:
+    """Have forward calls from this thread record ``events`` (six
+    ``torch.cuda.Event(enable_timing=True)``, already recorded once so their
+    handles exist) around the five stages; ``None`` switches it off."""
+    if not events:
+        _check(load().mb200_set_stage_events(None, 0), "set_stage_events")
+        return
+    arr = (ctypes.c_void_p * len(events))(*[ev.cuda_event for ev in events])
+    _check(load().mb200_set_stage_events(arr, len(events)), "set_stage_events")

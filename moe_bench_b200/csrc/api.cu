@@ -11,6 +11,13 @@ namespace mb200 {
 
 namespace {
 thread_local char g_last_error[512] = "";
+constexpr int kStageEvents = 6;
+thread_local cudaEvent_t g_stage_events[kStageEvents] = {};
+thread_local int g_stage_event_count = 0;
+
+inline void mark_stage(int i, cudaStream_t s) {
+  if (i < g_stage_event_count && g_stage_events[i]) cudaEventRecord(g_stage_events[i], s);
+}
 }
 
 void set_last_error(const char* fmt, ...) {
@@ -247,15 +254,31 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
   __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(ws + l.act);
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);
 
+  mark_stage(0, s);
   if ((rc = launch_align(topk_ids, tokens * topk, expert_map, local_experts, sched, cap,
                          reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
+  mark_stage(1, s);
   if ((rc = launch_gather_rows_bf16(reinterpret_cast<const __nv_bfloat16*>(hidden_states), sched, local_experts,
                                     topk, hidden, xg, cap, s))) return rc;
+  mark_stage(2, s);
   if ((rc = run_gemm_stage(kGateUpSwiglu, xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, nullptr, act, status, device, s))) return rc;
+  mark_stage(3, s);
   if ((rc = run_gemm_stage(kDownWeighted, act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s))) return rc;
-  return launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
+  mark_stage(4, s);
+  rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
+  mark_stage(5, s);
+  return rc;
+}
+
+int mb200_set_stage_events(void* const* events, int count) {
+  MB200_REQUIRE(count >= 0 && count <= kStageEvents && (count == 0 || events), kInvalidArgument,
+                "set_stage_events: count=%d (0..%d)", count, kStageEvents);
+  for (int i = 0; i < kStageEvents; ++i)
+    g_stage_events[i] = i < count ? reinterpret_cast<cudaEvent_t>(events[i]) : nullptr;
+  g_stage_event_count = count;
+  return kOk;
 }
 
 int mb200_read_status(const void* workspace, int32_t* status_out, void* stream) {
