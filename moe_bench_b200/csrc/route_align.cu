@@ -207,12 +207,14 @@ __global__ void align_scan_kernel(int* unit_hist, int units, int local_experts, 
   scan_units_and_experts(unit_hist, units, local_experts, counts, mtile_prefix, tiles_smem);
 }
 
+// Mark the padding rows of expert e with -1; `lane`/`width` are the caller's
+// position in the group of threads that shares the expert.
 __device__ __forceinline__ void fill_padding(const int* counts, const int* mtile_prefix, int e,
-                                             int* sorted_ids, int64_t row_capacity) {
+                                             int* sorted_ids, int64_t row_capacity, int lane, int width) {
   const int64_t begin = int64_t(mtile_prefix[e]) * kTileM + counts[e];
   int64_t end = int64_t(mtile_prefix[e + 1]) * kTileM;
   if (end > row_capacity) end = row_capacity;
-  for (int64_t p = begin + threadIdx.x; p < end; p += blockDim.x) sorted_ids[p] = -1;
+  for (int64_t p = begin + lane; p < end; p += width) sorted_ids[p] = -1;
 }
 
 __global__ void align_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ expert_map,
@@ -221,8 +223,9 @@ __global__ void align_scatter_kernel(const int* __restrict__ topk_ids, const int
                                      const int* __restrict__ mtile_prefix, int* __restrict__ sorted_ids,
                                      int* __restrict__ inverse, int64_t row_capacity) {
   extern __shared__ int hist_smem[];
-  for (int e = blockIdx.x; e < local_experts; e += gridDim.x)
-    fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity);
+  // one warp per expert, experts strided over every warp of the grid
+  for (int e = blockIdx.x * kAlignWarps + (threadIdx.x >> 5); e < local_experts; e += gridDim.x * kAlignWarps)
+    fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity, threadIdx.x & 31, 32);
 
   const int warp = threadIdx.x >> 5;
   const int unit = blockIdx.x * kAlignWarps + warp;
@@ -267,7 +270,8 @@ align_fused_kernel(const int* __restrict__ topk_ids, const int* __restrict__ exp
   __syncthreads();
   scan_units_and_experts(unit_hist, kFusedWarps, local_experts, counts, mtile_prefix, tiles_smem);
   __syncthreads();
-  for (int e = 0; e < local_experts; ++e) fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity);
+  for (int e = warp; e < local_experts; e += kFusedWarps)
+    fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity, threadIdx.x & 31, 32);
   for (int e = threadIdx.x & 31; e < local_experts; e += 32) running[e] = 0;
   __syncwarp();
   const int* base = unit_hist + size_t(warp) * local_experts;
