@@ -65,6 +65,39 @@ int mb200_align(const int32_t* topk_ids, int64_t tokens, int topk, const int32_t
                 int local_experts, int32_t* counts, int32_t* mtile_prefix, int32_t* sorted_ids,
                 int32_t* inverse, int64_t row_capacity, void* scratch, void* stream);
 
+/* mb200_align for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference.
+ *
+ * Who needs it: a serving process that gave all of HBM to its own memory pool
+ * at start-up cannot get a scratch buffer from cudaMalloc later, and a decode
+ * loop with a latency budget cannot afford the device-wide stall a
+ * cudaMalloc/cudaFree causes.  Here the sort's scratch (per-unit expert
+ * histograms) is a fixed 1 MiB array inside the library, so the caller passes
+ * only inputs and outputs and the call allocates nothing (no cudaMalloc,
+ * cudaFree or allocating library routine).
+ *
+ * Limits and rules:
+ *  - local_experts <= MB200_NOALLOC_MAX_LOCAL_EXPERTS and tokens*topk <=
+ *    MB200_NOALLOC_MAX_ASSIGNMENTS; larger problems are refused with status 5
+ *    and a message naming mb200_align as the alternative;
+ *  - every GPU that loads the library holds the 1 MiB array until the process
+ *    exits, whether or not this entry point is used;
+ *  - the first call on a device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call
+ *    before starting any stream capture;
+ *  - all calls on one device share the array, which keeps whatever the last call
+ *    left in it (nothing needs clearing: each call overwrites what it reads).
+ *    Calls that can overlap on the GPU (different streams, or concurrent host
+ *    threads) race on it; serialise them, or use mb200_align with one scratch
+ *    buffer per stream.
+ * Arguments and outputs are those of mb200_align. */
+#define MB200_NOALLOC_MAX_LOCAL_EXPERTS 256
+#define MB200_NOALLOC_MAX_ASSIGNMENTS 1048576
+int mb200_align_noalloc(const int32_t* topk_ids, int64_t tokens, int topk,
+                        const int32_t* expert_map, int local_experts, int32_t* counts,
+                        int32_t* mtile_prefix, int32_t* sorted_ids, int32_t* inverse,
+                        int64_t row_capacity, void* stream);
+
 /* Dynamic activation quantisation, one fp32 scale per row per 128 elements
  * (reference.py:143-145 -> vLLM per_token_group_quant_fp8).
  * x [rows, hidden] bf16 -> q [rows, hidden] e4m3, scales [rows, hidden/128]. */

@@ -30,6 +30,7 @@ SIGNATURES = {
     "mb200_row_capacity": (c_i64, [c_i64, c_i32, c_i32]),
     "mb200_align_scratch_bytes": (c_i64, [c_i64, c_i32, c_i32]),
     "mb200_align": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
+    "mb200_align_noalloc": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp]),
     "mb200_group_quant_fp8": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
     "mb200_grouped_gemm_bf16": (
         c_i32,
@@ -127,6 +128,41 @@ def align(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], local_expe
             _ptr(sorted_ids), _ptr(inverse), cap, _ptr(scratch), _stream(dev),
         ),
         "align",
+    )
+    return counts, prefix, sorted_ids, inverse[: t * k]
+
+
+def align_noalloc(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], local_experts: int, outputs=None):
+    """Sort-and-pad through the entry point that needs no scratch buffer.
+
+    For hosts that may not allocate device memory while running (a server
+    whose pool owns all of HBM, a latency-bound decode loop): the library's
+    built-in 1 MiB array replaces the scratch tensor.  Pass ``outputs`` =
+    ``(counts, mtile_prefix, sorted_ids, inverse)`` preallocated to make the
+    whole call allocation-free; without it the four output tensors are created
+    here for convenience.  Limits: 256 local experts, 2**20 assignments; calls
+    on one device must not overlap.
+    """
+    _need(topk_ids, torch.int32, "topk_ids")
+    if expert_map is not None:
+        _need(expert_map, torch.int32, "expert_map")
+    t, k = topk_ids.shape
+    dev = topk_ids.device
+    if outputs is None:
+        cap = row_capacity(t, k, local_experts)
+        outputs = (
+            torch.empty(local_experts, dtype=torch.int32, device=dev),
+            torch.empty(local_experts + 1, dtype=torch.int32, device=dev),
+            torch.full((cap,), -2, dtype=torch.int32, device=dev),
+            torch.empty(max(t * k, 1), dtype=torch.int32, device=dev),
+        )
+    counts, prefix, sorted_ids, inverse = outputs
+    _check(
+        load().mb200_align_noalloc(
+            _ptr(topk_ids), t, k, _ptr(expert_map), local_experts, _ptr(counts), _ptr(prefix),
+            _ptr(sorted_ids), _ptr(inverse), sorted_ids.shape[0], _stream(dev),
+        ),
+        "align_noalloc",
     )
     return counts, prefix, sorted_ids, inverse[: t * k]
 

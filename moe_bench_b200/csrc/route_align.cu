@@ -341,3 +341,84 @@ int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map
 }
 
 }  // namespace mb200
+
+// ---------------------------------------------------------------------------
+// Sort-and-pad without caller-provided scratch.
+//
+// Some hosts of this library must not allocate device memory once they are
+// running: an inference server that handed (nearly) all HBM to its own pool at
+// start-up has nothing left for a later cudaMalloc, and inside a latency-
+// critical decode loop cudaMalloc/cudaFree would stall the whole device.  For
+// them the unit histograms of the sort live in the fixed array below instead of
+// a buffer the caller allocates.  The price: 1 MiB of every GPU that loads the
+// library is held until the process exits, the problem size is capped, and all
+// calls on a device share the one array.
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+#include "../../include/moe_bench_b200.h"
+
+namespace mb200 {
+namespace {
+
+constexpr int kNoAllocMaxExperts = MB200_NOALLOC_MAX_LOCAL_EXPERTS;          // 256
+constexpr int64_t kNoAllocMaxAssignments = MB200_NOALLOC_MAX_ASSIGNMENTS;    // 2^20
+// units (<= 1024) x experts (<= 256) histogram entries = 1 MiB
+static __device__ __align__(256) int g_noalloc_align_scratch[kMaxUnits * kNoAllocMaxExperts];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+int* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {};
+
+// Device address of the array on the CURRENT device, looked up once per device.
+// In host code the array's name is only a handle for the runtime, never an
+// address a kernel may use, hence cudaGetSymbolAddress.
+int noalloc_scratch(int** out) {
+  int dev = -1;
+  MB200_CHECK_CUDA(cudaGetDevice(&dev));
+  MB200_REQUIRE(dev >= 0 && dev < kNoAllocMaxDevices, kUnsupportedShape,
+                "align_noalloc: device index %d, supported 0..%d", dev, kNoAllocMaxDevices - 1);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_scratch_ptr[dev]) {
+    void* p = nullptr;
+    MB200_CHECK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_align_scratch));
+    g_noalloc_scratch_ptr[dev] = static_cast<int*>(p);
+  }
+  *out = g_noalloc_scratch_ptr[dev];
+  return kOk;
+}
+
+}  // namespace
+}  // namespace mb200
+
+extern "C" int mb200_align_noalloc(const int32_t* topk_ids, int64_t tokens, int topk,
+                                   const int32_t* expert_map, int local_experts, int32_t* counts,
+                                   int32_t* mtile_prefix, int32_t* sorted_ids, int32_t* inverse,
+                                   int64_t row_capacity, void* stream) {
+  using namespace mb200;
+  MB200_REQUIRE(tokens >= 0 && topk >= 1, kInvalidArgument, "align_noalloc: tokens=%lld topk=%d",
+                (long long)tokens, topk);
+  MB200_REQUIRE(local_experts >= 1 && local_experts <= kNoAllocMaxExperts, kUnsupportedShape,
+                "align_noalloc: %d local experts exceed the built-in scratch (at most %d); "
+                "use mb200_align with a caller-provided scratch buffer",
+                local_experts, kNoAllocMaxExperts);
+  const int64_t assignments = tokens * topk;
+  MB200_REQUIRE(assignments <= kNoAllocMaxAssignments, kUnsupportedShape,
+                "align_noalloc: %lld assignments exceed the built-in scratch (at most %lld); "
+                "use mb200_align with a caller-provided scratch buffer",
+                (long long)assignments, (long long)kNoAllocMaxAssignments);
+  MB200_REQUIRE(counts && mtile_prefix && sorted_ids && (tokens == 0 || (topk_ids && inverse)),
+                kInvalidArgument, "align_noalloc: null pointer");
+  const int64_t touched = assignments < local_experts ? assignments : local_experts;
+  const int64_t need = (assignments + touched * (kTileM - 1) + kTileM - 1) / kTileM * kTileM;
+  MB200_REQUIRE(row_capacity >= need, kWorkspaceTooSmall, "align_noalloc: row capacity %lld < %lld",
+                (long long)row_capacity, (long long)need);
+  int* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  // Every histogram entry a launch reads is written earlier by the same launch
+  // sequence, so nothing left over from the previous call has to be cleared.
+  Schedule s{counts, mtile_prefix, sorted_ids, inverse};
+  return launch_align(topk_ids, assignments, expert_map, local_experts, s, row_capacity, scratch,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
