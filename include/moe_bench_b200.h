@@ -135,6 +135,30 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
                            int intermediate, int local_experts, int topk, void* workspace,
                            int64_t workspace_bytes, int device, void* stream);
 
+/* fp8 counterpart of mb200_grouped_gemm_bf16 (reference.py:65-95 block matmul).
+ * a: e4m3 [row_capacity, K] sorted rows; a_scale_t: fp32 [K/128][row_capacity]
+ * (group-major); w: e4m3 weights; w_scale: fp32 [E, rows/128, K/128].
+ * mode 0 writes out = e4m3 [row_capacity, N] (SiLU(gate)*up rounded to bf16, then
+ * re-quantised per row per 128, reference.py:156-163) and out_scale_t
+ * [N/128][row_capacity]; mode 1 writes out = bf16 [tokens*topk, hidden] scaled by
+ * row_scale. */
+int mb200_grouped_gemm_fp8(int mode, const void* a, const float* a_scale_t, int64_t row_capacity,
+                           const void* w, const float* w_scale, int local_experts, int hidden,
+                           int intermediate, const int32_t* counts, const int32_t* mtile_prefix,
+                           const int32_t* sorted_ids, const float* row_scale, void* out,
+                           float* out_scale_t, int32_t* status, int device, void* stream);
+
+/* The layer forward with fp8 block-quantised weights (reference.py:119-167 +
+ * 170-182; baseline.py:62-76 with quant_config).  w1/w2 are e4m3 with fp32
+ * scales w1_scale [E_local, 2*intermediate/128, hidden/128] and w2_scale
+ * [E_local, hidden/128, intermediate/128]; hidden_states and out are bf16.
+ * Activations are quantised per token per 128 elements on the fly. */
+int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void* w2,
+                          const float* w1_scale, const float* w2_scale, const int32_t* topk_ids,
+                          const float* topk_weights, const int32_t* expert_map, void* out,
+                          int64_t tokens, int hidden, int intermediate, int local_experts, int topk,
+                          void* workspace, int64_t workspace_bytes, int device, void* stream);
+
 /* Per-stage timing hook for benchmarks.  After mb200_set_stage_events(ev, 6) the
  * forward entry points called from this thread record ev[0] before the first
  * stage and ev[1..5] after the sort-and-pad, row gather, gate/up GEMM, down GEMM

@@ -41,6 +41,16 @@ SIGNATURES = {
         c_i32,
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64, c_i32, c_vp],
     ),
+    "mb200_grouped_gemm_fp8": (
+        c_i32,
+        [c_i32, c_vp, c_vp, c_i64, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+         c_i32, c_vp],
+    ),
+    "mb200_moe_forward_fp8": (
+        c_i32,
+        [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64,
+         c_i32, c_vp],
+    ),
     "mb200_set_stage_events": (c_i32, [c_vp, c_i32]),
     "mb200_read_status": (c_i32, [c_vp, c_vp, c_vp]),
 }
@@ -201,6 +211,35 @@ def moe_forward_bf16(x, w1, w2, topk_ids, topk_weights, expert_map, out, workspa
             dev.index or 0, _stream(dev),
         ),
         "moe_forward_bf16",
+    )
+
+
+def grouped_gemm_fp8(mode, a, a_scale_t, w, w_scale, hidden, intermediate, counts, prefix, sorted_ids,
+                     row_scale, out, out_scale_t, status):
+    """One fp8 grouped GEMM stage (mode 0 gate/up + SiLU-mul + re-quantise, mode 1 down + weight)."""
+    dev = a.device
+    _check(
+        load().mb200_grouped_gemm_fp8(
+            mode, _ptr(a), _ptr(a_scale_t), a.shape[0], _ptr(w), _ptr(w_scale), w.shape[0], hidden, intermediate,
+            _ptr(counts), _ptr(prefix), _ptr(sorted_ids), _ptr(row_scale), _ptr(out), _ptr(out_scale_t),
+            _ptr(status), dev.index or 0, _stream(dev),
+        ),
+        "grouped_gemm_fp8",
+    )
+
+
+def moe_forward_fp8(x, w1, w2, w1_scale, w2_scale, topk_ids, topk_weights, expert_map, out, workspace):
+    """Enqueue the fp8 block-quantised layer forward on the current stream."""
+    t, hidden = x.shape
+    e_local, two_n, _ = w1.shape
+    dev = x.device
+    _check(
+        load().mb200_moe_forward_fp8(
+            _ptr(x), _ptr(w1), _ptr(w2), _ptr(w1_scale), _ptr(w2_scale), _ptr(topk_ids), _ptr(topk_weights),
+            _ptr(expert_map), _ptr(out), t, hidden, two_n // 2, e_local, topk_ids.shape[1], _ptr(workspace),
+            workspace.numel(), dev.index or 0, _stream(dev),
+        ),
+        "moe_forward_fp8",
     )
 
 

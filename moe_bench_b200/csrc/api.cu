@@ -87,12 +87,13 @@ int64_t row_capacity(int64_t tokens, int topk, int local_experts) {
 
 struct Layout {
   int64_t status, counts, prefix, sorted, inverse, scratch, xg, act, y, total;
+  int64_t xs, acts;  // fp8 only: transposed activation scales [K/128][cap], [N/128][cap]
 };
 
 int64_t align_up(int64_t v) { return (v + 1023) / 1024 * 1024; }
 
 Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk) {
-  (void)precision;
+  const int64_t eb = precision == MB200_PRECISION_FP8 ? 1 : 2;  // bytes per activation element
   const int64_t a = tokens * topk;
   const int64_t cap = row_capacity(tokens, topk, local_experts);
   Layout l;
@@ -104,9 +105,14 @@ Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, 
   l.sorted = take(cap * 4);
   l.inverse = take((a > 0 ? a : 1) * 4);
   l.scratch = take(align_scratch_ints(a, local_experts) * 4);
-  l.xg = take(cap * hidden * 2);
-  l.act = take(cap * intermediate * 2);
+  l.xg = take(cap * hidden * eb);
+  l.act = take(cap * intermediate * eb);
   l.y = take((a > 0 ? a : 1) * int64_t(hidden) * 2);
+  l.xs = l.acts = 0;
+  if (precision == MB200_PRECISION_FP8) {
+    l.xs = take(int64_t(hidden / 128) * cap * 4);
+    l.acts = take(int64_t(intermediate / 128) * cap * 4);
+  }
   l.total = off;
   return l;
 }
@@ -156,6 +162,55 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
     g.out_cols = hidden;
   }
   return launch_grouped_gemm_bf16(GemmMode(mode), map_a, map_b, g, device, stream);
+}
+
+int check_shape_fp8(int hidden, int intermediate) {
+  MB200_REQUIRE(hidden % 128 == 0 && intermediate % 128 == 0, kUnsupportedShape,
+                "fp8: hidden=%d and intermediate=%d must be multiples of the 128x128 scale block", hidden,
+                intermediate);
+  return kOk;
+}
+
+int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
+                       const float* w_scale, int local_experts, int hidden, int intermediate,
+                       const int* counts, const int* prefix, const int* sorted, const float* row_scale,
+                       void* out, float* out_scale_t, int* status, int device, cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  GemmFp8Args g{};
+  g.counts = counts;
+  g.mtile_prefix = prefix;
+  g.sorted_ids = sorted;
+  g.num_experts = local_experts;
+  g.row_capacity = cap;
+  g.a_scale_t = a_scale_t;
+  g.w_scale = w_scale;
+  g.row_scale = row_scale;
+  g.out = out;
+  g.out_scale_t = out_scale_t;
+  g.status = status;
+  int rc;
+  if (mode == kGateUpSwiglu) {
+    if ((rc = make_tensor_map_2d(&map_a, a, 1, uint64_t(cap), uint64_t(hidden), kTileM))) return rc;
+    if ((rc = make_tensor_map_2d(&map_b, w, 1, uint64_t(local_experts) * 2 * intermediate, uint64_t(hidden), 128))) return rc;
+    g.n_tiles = intermediate / 128;
+    g.k_blocks = hidden / 128;
+    g.b_rows_per_expert = 2 * intermediate;
+    g.b_half_offset = intermediate;
+    g.out_cols = intermediate;
+    g.scale_rows_per_expert = 2 * intermediate / 128;
+    g.scale_half_offset = intermediate / 128;
+  } else {
+    if ((rc = make_tensor_map_2d(&map_a, a, 1, uint64_t(cap), uint64_t(intermediate), kTileM))) return rc;
+    if ((rc = make_tensor_map_2d(&map_b, w, 1, uint64_t(local_experts) * hidden, uint64_t(intermediate), 256))) return rc;
+    g.n_tiles = (hidden + 255) / 256;
+    g.k_blocks = intermediate / 128;
+    g.b_rows_per_expert = hidden;
+    g.b_half_offset = 0;
+    g.out_cols = hidden;
+    g.scale_rows_per_expert = hidden / 128;
+    g.scale_half_offset = 0;
+  }
+  return launch_grouped_gemm_fp8(GemmMode(mode), map_a, map_b, g, device, stream);
 }
 
 }  // namespace
@@ -222,10 +277,11 @@ int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_cap, const void
 int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
                               int local_experts, int topk) {
   if (check_shape(tokens, hidden, intermediate, local_experts, topk)) return -1;
-  if (precision != MB200_PRECISION_BF16) {
-    set_last_error("workspace_bytes: precision %d is not built", precision);
+  if (precision != MB200_PRECISION_BF16 && precision != MB200_PRECISION_FP8) {
+    set_last_error("workspace_bytes: unknown precision %d", precision);
     return -1;
   }
+  if (precision == MB200_PRECISION_FP8 && check_shape_fp8(hidden, intermediate)) return -1;
   return make_layout(precision, tokens, hidden, intermediate, local_experts, topk).total;
 }
 
@@ -266,6 +322,73 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
   mark_stage(3, s);
   if ((rc = run_gemm_stage(kDownWeighted, act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s))) return rc;
+  mark_stage(4, s);
+  rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
+  mark_stage(5, s);
+  return rc;
+}
+
+int mb200_grouped_gemm_fp8(int mode, const void* a, const float* a_scale_t, int64_t row_cap, const void* w,
+                           const float* w_scale, int local_experts, int hidden, int intermediate,
+                           const int32_t* counts, const int32_t* mtile_prefix, const int32_t* sorted_ids,
+                           const float* row_scale, void* out, float* out_scale_t, int32_t* status,
+                           int device, void* stream) {
+  MB200_REQUIRE(mode == 0 || mode == 1, kInvalidArgument, "grouped_gemm_fp8: mode=%d", mode);
+  MB200_REQUIRE(a && a_scale_t && w && w_scale && counts && mtile_prefix && sorted_ids && out &&
+                    (mode == 0 ? out_scale_t != nullptr : row_scale != nullptr),
+                kInvalidArgument, "grouped_gemm_fp8: null pointer");
+  MB200_REQUIRE(row_cap > 0 && row_cap % kTileM == 0, kInvalidArgument,
+                "grouped_gemm_fp8: row capacity %lld must be a positive multiple of %d", (long long)row_cap, kTileM);
+  int rc = check_shape(0, hidden, intermediate, local_experts, 1);
+  if (rc) return rc;
+  if ((rc = check_shape_fp8(hidden, intermediate))) return rc;
+  return run_gemm_stage_fp8(mode, a, a_scale_t, row_cap, w, w_scale, local_experts, hidden, intermediate, counts,
+                            mtile_prefix, sorted_ids, row_scale, out, out_scale_t, status, device,
+                            as_stream(stream));
+}
+
+int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void* w2, const float* w1_scale,
+                          const float* w2_scale, const int32_t* topk_ids, const float* topk_weights,
+                          const int32_t* expert_map, void* out, int64_t tokens, int hidden, int intermediate,
+                          int local_experts, int topk, void* workspace, int64_t workspace_bytes, int device,
+                          void* stream) {
+  int rc = check_shape(tokens, hidden, intermediate, local_experts, topk);
+  if (rc) return rc;
+  if ((rc = check_shape_fp8(hidden, intermediate))) return rc;
+  if (tokens == 0) return kOk;
+  MB200_REQUIRE(hidden_states && w1 && w2 && w1_scale && w2_scale && topk_ids && topk_weights && out && workspace,
+                kInvalidArgument, "moe_forward_fp8: null pointer");
+  const Layout l = make_layout(MB200_PRECISION_FP8, tokens, hidden, intermediate, local_experts, topk);
+  MB200_REQUIRE(workspace_bytes >= l.total, kWorkspaceTooSmall, "moe_forward_fp8: workspace %lld < %lld bytes",
+                (long long)workspace_bytes, (long long)l.total);
+  MB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, kInvalidArgument,
+                "moe_forward_fp8: workspace must be 1024-byte aligned");
+  cudaStream_t s = as_stream(stream);
+  char* ws = reinterpret_cast<char*>(workspace);
+  int* status = reinterpret_cast<int*>(ws + l.status);
+  Schedule sched{reinterpret_cast<int*>(ws + l.counts), reinterpret_cast<int*>(ws + l.prefix),
+                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse)};
+  const int64_t cap = row_capacity(tokens, topk, local_experts);
+  uint8_t* xq = reinterpret_cast<uint8_t*>(ws + l.xg);
+  float* xs_t = reinterpret_cast<float*>(ws + l.xs);
+  uint8_t* actq = reinterpret_cast<uint8_t*>(ws + l.act);
+  float* acts_t = reinterpret_cast<float*>(ws + l.acts);
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);
+
+  mark_stage(0, s);
+  if ((rc = launch_align(topk_ids, tokens * topk, expert_map, local_experts, sched, cap,
+                         reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
+  mark_stage(1, s);
+  if ((rc = launch_gather_quant_fp8(reinterpret_cast<const __nv_bfloat16*>(hidden_states), sched, local_experts,
+                                    topk, hidden, xq, xs_t, cap, s))) return rc;
+  mark_stage(2, s);
+  if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, xq, xs_t, cap, w1, w1_scale, local_experts, hidden, intermediate,
+                               sched.counts, sched.mtile_prefix, sched.sorted_ids, nullptr, actq, acts_t, status,
+                               device, s))) return rc;
+  mark_stage(3, s);
+  if ((rc = run_gemm_stage_fp8(kDownWeighted, actq, acts_t, cap, w2, w2_scale, local_experts, hidden, intermediate,
+                               sched.counts, sched.mtile_prefix, sched.sorted_ids, topk_weights, y, nullptr, status,
+                               device, s))) return rc;
   mark_stage(4, s);
   rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
   mark_stage(5, s);

@@ -36,6 +36,10 @@ int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, 
 // Per-row, per-128-group e4m3 quantisation.  scales_t is [K/128][scale_ld] (group-major).
 int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uint8_t* q,
                            float* scales, int64_t scale_ld, int transposed, cudaStream_t stream);
+// Gather + quantise: xq[row] = e4m3(x[token(row)]), scales_t[g][row] for the sorted rows.
+int launch_gather_quant_fp8(const __nv_bfloat16* x, const Schedule& sched, int local_experts,
+                            int topk, int hidden, uint8_t* xq, float* scales_t,
+                            int64_t row_capacity, cudaStream_t stream);
 
 // ---- grouped_gemm.cu -----------------------------------------------------------------
 struct GemmArgs {
@@ -55,6 +59,30 @@ struct GemmArgs {
 enum GemmMode : int { kGateUpSwiglu = 0, kDownWeighted = 1 };
 int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_a, const CUtensorMap& map_b,
                              const GemmArgs& args, int device, cudaStream_t stream);
+
+// grouped_gemm_fp8.cu: e4m3 operands, fp32 block scales applied in the epilogue
+struct GemmFp8Args {
+  const int* counts;
+  const int* mtile_prefix;
+  const int* sorted_ids;
+  int num_experts;
+  int n_tiles;
+  int k_blocks;               // K / 128
+  int b_rows_per_expert;
+  int b_half_offset;
+  int out_cols;
+  int64_t row_capacity;       // leading dimension of the transposed scale arrays
+  const float* a_scale_t;     // [k_blocks][row_capacity] activation scales
+  const float* w_scale;       // [E][scale_rows_per_expert][k_blocks] weight block scales
+  int scale_rows_per_expert;
+  int scale_half_offset;      // gate/up: scale row of the up half
+  void* out;                  // gate/up: e4m3 [rows][N]; down: bf16 [assignments][hidden]
+  float* out_scale_t;         // gate/up: [N/128][row_capacity]
+  const float* row_scale;     // down: combine weights
+  int* status;
+};
+int launch_grouped_gemm_fp8(GemmMode mode, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                            const GemmFp8Args& args, int device, cudaStream_t stream);
 
 // ---- tensormap.cu ----------------------------------------------------------------------
 // Row-major 2-D tensor [rows][cols] of elem_bytes elements, boxes of

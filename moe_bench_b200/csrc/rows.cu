@@ -66,6 +66,38 @@ __global__ void combine_bf16_kernel(const uint4* __restrict__ y, const int* __re
   }
 }
 
+// Quantise the 16 elements a thread holds of a 128-wide group shared by 8
+// consecutive lanes; returns the group's scale (identical in the 8 lanes).
+__device__ __forceinline__ float quantize_slice16(const uint4& a, const uint4& b, uint32_t (&w)[4]) {
+  float f[16];
+  const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 fa = __bfloat1622float2(ha[i]), fb = __bfloat1622float2(hb[i]);
+    f[2 * i] = fa.x; f[2 * i + 1] = fa.y; f[8 + 2 * i] = fb.x; f[8 + 2 * i + 1] = fb.y;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+  const unsigned group_mask = 0xFFu << (threadIdx.x & 24);  // the 8 lanes sharing this group
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, o));
+  amax = fmaxf(amax, 1e-10f);
+  const float scale = __fdiv_rn(amax, 448.0f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float qv = fminf(fmaxf(__fdiv_rn(f[4 * i + j], scale), -448.f), 448.f);
+      packed |= uint32_t(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+    }
+    w[i] = packed;
+  }
+  return scale;
+}
+
 // One 128-wide group per 8 lanes (16 bf16 each).
 __global__ void group_quant_fp8_kernel(const uint4* __restrict__ x, int64_t rows, int groups_per_row,
                                        uint2* __restrict__ q, float* __restrict__ scales,
@@ -74,36 +106,9 @@ __global__ void group_quant_fp8_kernel(const uint4* __restrict__ x, int64_t rows
   const int sub = threadIdx.x & 7;
   for (int64_t g = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3; g < total_groups;
        g += (int64_t(gridDim.x) * blockDim.x) >> 3) {
-    // 16 elements = two 16-byte loads
-    const uint4* src = x + g * 16 + sub * 2;
-    uint4 a = __ldg(src), b = __ldg(src + 1);
-    float f[16];
-    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
-    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 fa = __bfloat1622float2(ha[i]), fb = __bfloat1622float2(hb[i]);
-      f[2 * i] = fa.x; f[2 * i + 1] = fa.y; f[8 + 2 * i] = fb.x; f[8 + 2 * i + 1] = fb.y;
-    }
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
-    const unsigned group_mask = 0xFFu << (threadIdx.x & 24);  // the 8 lanes sharing this group
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, o));
-    amax = fmaxf(amax, 1e-10f);
-    const float scale = amax * (1.0f / 448.0f);
+    const uint4* src = x + g * 16 + sub * 2;  // 16 elements = two 16-byte loads
     uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t packed = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float qv = fminf(fmaxf(__fdiv_rn(f[4 * i + j], scale), -448.f), 448.f);
-        packed |= uint32_t(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
-      }
-      w[i] = packed;
-    }
+    const float scale = quantize_slice16(__ldg(src), __ldg(src + 1), w);
     uint2* dst = q + g * 16 + sub * 2;
     dst[0] = make_uint2(w[0], w[1]);
     dst[1] = make_uint2(w[2], w[3]);
@@ -112,6 +117,39 @@ __global__ void group_quant_fp8_kernel(const uint4* __restrict__ x, int64_t rows
       const int64_t grp = g - row * groups_per_row;
       if (transposed) scales[grp * scale_ld + row] = scale;
       else scales[row * scale_ld + grp] = scale;
+    }
+  }
+}
+
+// Sorted rows: gather the token's row and quantise it in one pass (one warp per
+// row, four groups per step).  Scales are stored group-major so the GEMM's
+// epilogue threads (one row each) read them coalesced.
+__global__ void gather_quant_fp8_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted_ids,
+                                        const int* __restrict__ mtile_prefix, int local_experts,
+                                        int topk, int groups_per_row, uint2* __restrict__ xq,
+                                        float* __restrict__ scales_t, int64_t row_capacity) {
+  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * kTileM;
+  if (rows > row_capacity) rows = row_capacity;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & 7;
+  for (int64_t row = int64_t(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += int64_t(gridDim.x) * warps_per_block) {
+    const int n = __ldg(sorted_ids + row);
+    if (n < 0) continue;
+    const uint4* src_row = x + int64_t(n / topk) * groups_per_row * 16;
+    uint2* dst_row = xq + row * groups_per_row * 16;
+    for (int g0 = 0; g0 < groups_per_row; g0 += 4) {
+      const int g = g0 + (lane >> 3);
+      if (g < groups_per_row) {  // whole 8-lane groups take this branch together
+        const uint4* src = src_row + g * 16 + sub * 2;
+        uint32_t w[4];
+        const float scale = quantize_slice16(__ldg(src), __ldg(src + 1), w);
+        uint2* dst = dst_row + g * 16 + sub * 2;
+        dst[0] = make_uint2(w[0], w[1]);
+        dst[1] = make_uint2(w[2], w[3]);
+        if (sub == 0) scales_t[int64_t(g) * row_capacity + row] = scale;
+      }
     }
   }
 }
@@ -171,6 +209,19 @@ int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uin
   group_quant_fp8_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(x), rows,
                                                         hidden / 128, reinterpret_cast<uint2*>(q), scales,
                                                         scale_ld, transposed);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_gather_quant_fp8(const __nv_bfloat16* x, const Schedule& sched, int local_experts, int topk,
+                            int hidden, uint8_t* xq, float* scales_t, int64_t row_capacity,
+                            cudaStream_t stream) {
+  MB200_REQUIRE(hidden % 128 == 0, kUnsupportedShape, "gather_quant: hidden=%d must be a multiple of 128", hidden);
+  const int threads = 256;
+  const int blocks = grid_for(row_capacity * 32, threads, sm_count(), 16);
+  gather_quant_fp8_kernel<<<blocks, threads, 0, stream>>>(
+      reinterpret_cast<const uint4*>(x), sched.sorted_ids, sched.mtile_prefix, local_experts, topk,
+      hidden / 128, reinterpret_cast<uint2*>(xq), scales_t, row_capacity);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -38,7 +38,9 @@ class MoEImplementation(ABC):
 
 class B200FusedExperts(MoEImplementation):
     """MoE layer forward on hand-written sm_100a kernels (tcgen05 grouped GEMMs
-    fed by TMA, fused SiLU-mul and combine weights) through the C ABI."""
+    fed by TMA, fused SiLU-mul, activation re-quantisation and combine weights)
+    through the C ABI; bf16, and fp8 with 128x128 weight-block / 1x128
+    activation-group fp32 scales."""
 
     name = "b200"
 
@@ -46,6 +48,8 @@ class B200FusedExperts(MoEImplementation):
         self._key = None
         self._workspace = None
         self._out = None
+        self._fp8 = False
+        self._w1_scale = self._w2_scale = None
 
     @staticmethod
     def _shape_key(problem: MoEProblem):
@@ -59,13 +63,27 @@ class B200FusedExperts(MoEImplementation):
         if not problem.hidden_states.is_cuda:
             raise capi.MB200Error("B200FusedExperts needs CUDA tensors; there is no CPU path")
         prec = Precision(problem.config.precision.value)
-        if prec != Precision.BF16:
-            raise capi.MB200Error(f"precision {prec.value} is not built in this library version")
+        if prec == Precision.FP16:
+            raise capi.MB200Error("precision fp16 is not built in this library version (bf16 and fp8 are)")
+        self._fp8 = prec == Precision.FP8
+        if self._fp8:
+            qc = problem.quant_config
+            if qc is None or qc.w1_scale is None or qc.w2_scale is None:
+                raise capi.MB200Error("fp8 problem without quant_config.w1_scale / w2_scale")
+            if list(qc.block_shape) != [128, 128]:
+                raise capi.MB200Error(f"fp8 block_shape {qc.block_shape} is not supported (only [128, 128])")
+            if problem.w1.dtype != torch.float8_e4m3fn:
+                raise capi.MB200Error(f"fp8 problem with {problem.w1.dtype} weights")
+            # plugin-owned contiguous fp32 copies of the (small) scale tables
+            self._w1_scale = qc.w1_scale.to(torch.float32).contiguous()
+            self._w2_scale = qc.w2_scale.to(torch.float32).contiguous()
         capi.load()
         t, hidden = problem.hidden_states.shape
         e_local, two_n, _ = problem.w1.shape
         topk = problem.topk_ids.shape[1]
-        nbytes = capi.workspace_bytes(capi.PRECISION_BF16, t, hidden, two_n // 2, e_local, topk)
+        nbytes = capi.workspace_bytes(
+            capi.PRECISION_FP8 if self._fp8 else capi.PRECISION_BF16, t, hidden, two_n // 2, e_local, topk
+        )
         dev = problem.hidden_states.device
         # torch's caching allocator hands out 512-byte aligned blocks; over-allocate
         # and slice to the 1024-byte boundary the tile buffers need.
@@ -80,10 +98,16 @@ class B200FusedExperts(MoEImplementation):
         if self._key != self._shape_key(problem):
             raise capi.MB200Error("run() called with a problem of another shape than setup()")
         expert_map = problem.expert_map
-        capi.moe_forward_bf16(
-            problem.hidden_states, problem.w1, problem.w2, problem.topk_ids, problem.topk_weights,
-            expert_map, self._out, self._workspace,
-        )
+        if self._fp8:
+            capi.moe_forward_fp8(
+                problem.hidden_states, problem.w1, problem.w2, self._w1_scale, self._w2_scale,
+                problem.topk_ids, problem.topk_weights, expert_map, self._out, self._workspace,
+            )
+        else:
+            capi.moe_forward_bf16(
+                problem.hidden_states, problem.w1, problem.w2, problem.topk_ids, problem.topk_weights,
+                expert_map, self._out, self._workspace,
+            )
         return self._out
 
     def device_status(self) -> int:

@@ -20,8 +20,10 @@ Parity status
   ``group_quant_fp8`` (cases ``config1_*_fp8`` of ``golden.pt``).  The activation
   quantiser itself is a call into vLLM 0.22.0 (``moe_kernel_quantize_input`` ->
   ``per_token_group_quant_fp8``), a third-party CUDA/Triton op that cannot run
-  on a CPU and that no reference test pins at bit level: for it this oracle is
-  "parity unpinned" bit-wise and tolerance-pinned through ``verify_output``.
+  on a CPU and that no reference test pins at bit level: on the CPU this oracle
+  is "parity unpinned" for it; on a GPU box the test-suite pins the CUDA
+  quantiser of this package (which must equal ``group_quant_fp8`` bit for bit)
+  against vLLM's op itself.
 * top-k routing (``route_topk``): the reference has no router (it draws ids
   directly, ``data.py:178-235``); the oracle is the textbook
   softmax -> top-k -> renormalise and is "parity unpinned".
@@ -107,16 +109,20 @@ def route_topk(logits: torch.Tensor, k: int):
 def group_quant_fp8(x: torch.Tensor, group: int = 128, eps: float = 1e-10):
     """Per-row, per-``group`` dynamic e4m3 quantisation of activations.
 
-    Published semantics of vLLM 0.22.0 ``per_token_group_quant_fp8``
-    (``model_executor/layers/quantization/utils/fp8_utils.py``; used by
-    reference.py:143-145,157-163): ``amax = max(|x|, eps)`` in fp32,
-    ``scale = amax * (1/448)``, ``q = clamp(x / scale, -448, 448)`` rounded to
-    nearest-even e4m3.  Returns ``(q (m, K) e4m3, scales (m, K/group) fp32)``.
+    Semantics of vLLM 0.22.0 ``per_token_group_quant_fp8`` as the reference
+    reaches it on a GPU (reference.py:143-145,157-163 -> the
+    ``per_token_group_fp8_quant`` CUDA op): ``amax = max(|x|, eps)`` in fp32,
+    ``scale = amax / 448`` (an IEEE division; vLLM's Triton fallback multiplies
+    by the reciprocal instead, which differs in the last bit for ~60 % of the
+    groups), ``q = clamp(x / scale, -448, 448)`` rounded to nearest-even e4m3.
+    The GPU test-suite compares the CUDA kernel of this package with vLLM's op
+    byte for byte where vLLM is installed.
+    Returns ``(q (m, K) e4m3, scales (m, K/group) fp32)``.
     """
     m, k = x.shape
     xf = x.float().view(m, k // group, group)
     amax = xf.abs().amax(dim=-1, keepdim=True).clamp_min(eps)
-    scale = amax * np.float32(1.0 / FP8_MAX)
+    scale = amax / np.float32(FP8_MAX)
     q = (xf / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
     return q.view(m, k), scale.view(m, k // group)
 
