@@ -172,12 +172,14 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line))
 
 
-def _config_dict(tokens: int, world: int):
+def _config_dict(tokens: int, world: int, precision: str = "bf16"):
+    wgb = 22.5 if precision == "bf16" else 11.3
     return {
-        "workload": f"dsv32_bf16_compute_only_T{tokens}" + ("" if EXPERTS == 256 else f"_E{EXPERTS}"), "tokens_per_gpu": tokens, "hidden": HIDDEN,
+        "workload": f"dsv32_{precision}_compute_only_T{tokens}" + ("" if EXPERTS == 256 else f"_E{EXPERTS}"),
+        "tokens_per_gpu": tokens, "hidden": HIDDEN,
         "intermediate": INTER, "experts": EXPERTS, "topk": TOPK, "routing": "uniform", "seed": 0,
         "parallelism": "single GPU" if world == 1 else f"{world} token-sharded replicas, all experts on every GPU",
-        "l2": "inputs larger than L2: 22.5 GB of expert weights are streamed every step",
+        "l2": f"inputs larger than L2: {wgb} GB of expert weights are streamed every step",
     }
 
 
@@ -198,10 +200,12 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         dist.init_process_group("nccl", device_id=dev)
 
     tokens, steps, warmup = args.tokens, args.steps, args.warmup
-    cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS)
+    fp8 = args.precision == "fp8"
+    cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS,
+                                precision=P.Precision.FP8 if fp8 else P.Precision.BF16)
     weights = P.make_weights(cfg)
     x, ids, wts = P._gen_input(cfg, tokens, rank)  # every rank its own token shard
-    prob = P.MoEProblem(cfg, tokens, x, weights.w1, weights.w2, ids, wts, None, None)
+    prob = P.MoEProblem(cfg, tokens, x, weights.w1, weights.w2, ids, wts, None, weights.quant_config)
     impl = get_implementation("b200")
     impl.setup(prob)
     assignments = tokens * TOPK
@@ -245,7 +249,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     if args.skip_extras:
         if rank == 0:
             print(json.dumps({"ms_per_step": ms_step, "stage_ms": dict(zip(capi.STAGE_NAMES, stage_ms)),
-                              "config": _config_dict(tokens, world), "note": "profiling run, extras skipped"}))
+                              "config": _config_dict(tokens, world, args.precision),
+                              "note": "profiling run, extras skipped"}))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -282,7 +287,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     idx = torch.randperm(tokens, generator=torch.Generator().manual_seed(0))[: min(8, tokens)].to(dev)
     sub = dataclasses.replace(prob, num_tokens=len(idx), hidden_states=x[idx].contiguous(),
                               topk_ids=ids[idx].contiguous(), topk_weights=wts[idx].contiguous())
-    check = O.verify_output("bf16", out[idx], O.reference_moe(sub))
+    check = O.verify_output(args.precision, out[idx], O.reference_moe(sub))
 
     if world > 1:
         ok = torch.tensor([1.0 if check.passed else 0.0], device=dev)
@@ -295,31 +300,34 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         peaks = _peaks()
         touched = _touched_experts(ids)
         rows = assignments  # real rows; padding rows are neither loaded with data nor stored
-        gemm_bytes = touched * 2 * INTER * HIDDEN * 2 + rows * HIDDEN * 2 + rows * INTER * 2
+        wb = 1 if fp8 else 2  # bytes per weight / activation element on the GEMM's operands
+        gemm_bytes = touched * 2 * INTER * HIDDEN * wb + rows * HIDDEN * wb + rows * INTER * wb
         gemm_flops = 4.0 * INTER * HIDDEN * assignments
         gemm_ms = stage_ms[2]
         t_hbm = gemm_bytes / (peaks["hbm_gbs"] * 1e9)
-        t_tc = gemm_flops / (peaks["bf16_tflops"] * 1e12)
+        # no fp8 peak is measured on this pool: the bf16 burst figure is doubled (nominal ratio)
+        tc_peak = peaks["bf16_tflops"] * (2.0 if fp8 else 1.0)
+        t_tc = gemm_flops / (tc_peak * 1e12)
         if t_hbm >= t_tc:
             roof = {"bound": "hbm", "achieved": gemm_bytes / (gemm_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                     "unit": "GB/s"}
         else:
             roof = {"bound": "tensor", "achieved": gemm_flops / (gemm_ms * 1e-3) / 1e12,
-                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s"}
+                    "peak": tc_peak, "unit": "TFLOP/s"}
         roof["frac"] = roof["achieved"] / roof["peak"]
         roof.update({
-            "traffic": None, "kernel": "grouped_gemm_bf16_kernel<gate_up_swiglu>", "kernel_ms": gemm_ms,
+            "traffic": None, "kernel": f"grouped_gemm_{args.precision}_kernel<gate_up_swiglu>", "kernel_ms": gemm_ms,
             "peak_source": peaks["source"] + " (burst)", "algorithmic_bytes": gemm_bytes,
             "algorithmic_flops": gemm_flops, "t_hbm_ms": t_hbm * 1e3, "t_tensor_ms": t_tc * 1e3,
         })
-        layer_bytes = touched * 3 * INTER * HIDDEN * 2 + 2 * tokens * HIDDEN * 2 + assignments * 8
-        layer_roof_ms = max(layer_bytes / (peaks["hbm_gbs"] * 1e9), flops_step / (peaks["bf16_tflops"] * 1e12)) * 1e3
+        layer_bytes = touched * 3 * INTER * HIDDEN * wb + 2 * tokens * HIDDEN * 2 + assignments * 8
+        layer_roof_ms = max(layer_bytes / (peaks["hbm_gbs"] * 1e9), flops_step / (tc_peak * 1e12)) * 1e3
         kernels_per_step = 7 if assignments > 16384 else 5
         line = {
             "metric": METRIC, "value": flops_step * world / (ms_step * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": _config_dict(tokens, world),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.precision,
+            "data": "synthetic", "config": _config_dict(tokens, world, args.precision),
             "e2e": {"value": flops_step * world / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": kernels_per_step * steps,
@@ -330,7 +338,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "latency_us": ms_step * 1e3,
             "verify": "ok" if passed else "FAIL", "rel_err": check.rel_err,
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not fp8:  # the CPU leg times the bf16 oracle
             res = _time_cpu_oracle(tokens, 20, 2)
             line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
@@ -346,6 +354,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=8192, help="tokens per GPU")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8"],
+                    help="bf16 = the headline workload; fp8 = the block-quantised config of the same shape")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--experts", type=int, default=256, help="expert count (lower it only to size a profiler capture)")
     ap.add_argument("--skip-extras", action="store_true", help="timed region only: no e2e, parity or CPU legs")

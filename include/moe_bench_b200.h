@@ -159,6 +159,51 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
                           int64_t tokens, int hidden, int intermediate, int local_experts, int topk,
                           void* workspace, int64_t workspace_bytes, int device, void* stream);
 
+/* ---- distributed layer: one process per GPU, peers' buffers mapped by the caller ----
+ *
+ * Replaces the serial scheme's AllGather -> fused_experts -> ReduceScatter
+ * (schemes.py:117-143) for both parallel modes of config.py:18-35:
+ *   expert_parallel = 1  rank r owns experts [r*E_local, (r+1)*E_local) (data.py:238-253)
+ *   expert_parallel = 0  tensor parallel: all experts, intermediate/world columns
+ * Every rank passes its own token shard (hidden_states [tokens, hidden], routing
+ * over GLOBAL expert ids) and receives its own rows of the combined output.
+ *
+ * symmetric_ptrs[world]: base pointers, valid in THIS process, of one buffer per
+ * rank with mb200_dist_symmetric_bytes() bytes, 1024-byte aligned, zero-filled
+ * once after allocation; entry [rank] is this rank's own buffer.  The library
+ * only loads from peers' buffers and stores 4-byte barrier flags into them.
+ * seq_base: a counter that is equal on all ranks and grows by
+ * MB200_DIST_SEQ_STRIDE per call (barrier sequence numbers are never reset).
+ * All ranks must make the same calls in the same order.  A barrier that does not
+ * complete within 3 s stores 150+peer in the workspace status word and the call's
+ * kernels carry on, so the context stays usable; the output is then undefined. */
+#define MB200_DIST_SEQ_STRIDE 4
+int64_t mb200_dist_symmetric_bytes(int precision, int64_t tokens, int hidden, int topk, int world);
+int64_t mb200_dist_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
+                                   int local_experts, int topk, int world);
+int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_states, const void* w1,
+                       const void* w2, const float* w1_scale, const float* w2_scale,
+                       const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
+                       void* out, int64_t tokens, int hidden, int intermediate, int local_experts,
+                       int global_experts, int topk, int rank, int world, void* const* symmetric_ptrs,
+                       int64_t symmetric_bytes, uint32_t seq_base, void* workspace, int64_t workspace_bytes,
+                       int device, void* stream);
+/* The all-rank barrier used inside mb200_dist_forward, exposed for set-up and
+ * tear-down (protocol of sm120_common.cuh:47-64, with a time limit). */
+int mb200_peer_barrier(void* const* symmetric_ptrs, int rank, int world, uint32_t seq, int32_t* status,
+                       void* stream);
+
+/* Set-up only: a zero-filled device buffer that other processes on the same box
+ * can map through CUDA IPC (for hosts without another way to share GPU memory;
+ * the reference's TK path uses a VMM/IPC broker, experience/11:13-21).  alloc
+ * returns the pointer and a 64-byte handle to send to the peers; open maps a
+ * peer's handle; close/free undo them.  These four are the only allocating
+ * entry points and are never called from the forward path. */
+int mb200_ipc_alloc(int64_t bytes, void** ptr_out, void* handle_out64);
+int mb200_ipc_open(const void* handle64, void** ptr_out);
+int mb200_ipc_close(void* ptr);
+int mb200_ipc_free(void* ptr);
+
 /* Per-stage timing hook for benchmarks.  After mb200_set_stage_events(ev, 6) the
  * forward entry points called from this thread record ev[0] before the first
  * stage and ev[1..5] after the sort-and-pad, row gather, gate/up GEMM, down GEMM

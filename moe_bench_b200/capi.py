@@ -51,6 +51,18 @@ SIGNATURES = {
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64,
          c_i32, c_vp],
     ),
+    "mb200_dist_symmetric_bytes": (c_i64, [c_i32, c_i64, c_i32, c_i32, c_i32]),
+    "mb200_dist_workspace_bytes": (c_i64, [c_i32, c_i64, c_i32, c_i32, c_i32, c_i32, c_i32]),
+    "mb200_dist_forward": (
+        c_i32,
+        [c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32,
+         c_i32, c_i32, c_i32, c_vp, c_i64, ctypes.c_uint32, c_vp, c_i64, c_i32, c_vp],
+    ),
+    "mb200_peer_barrier": (c_i32, [c_vp, c_i32, c_i32, ctypes.c_uint32, c_vp, c_vp]),
+    "mb200_ipc_alloc": (c_i32, [c_i64, c_vp, c_vp]),
+    "mb200_ipc_open": (c_i32, [c_vp, c_vp]),
+    "mb200_ipc_close": (c_i32, [c_vp]),
+    "mb200_ipc_free": (c_i32, [c_vp]),
     "mb200_set_stage_events": (c_i32, [c_vp, c_i32]),
     "mb200_read_status": (c_i32, [c_vp, c_vp, c_vp]),
 }
@@ -240,6 +252,49 @@ def moe_forward_fp8(x, w1, w2, w1_scale, w2_scale, topk_ids, topk_weights, exper
             workspace.numel(), dev.index or 0, _stream(dev),
         ),
         "moe_forward_fp8",
+    )
+
+
+DIST_SEQ_STRIDE = 4
+
+
+def dist_symmetric_bytes(precision: int, tokens: int, hidden: int, topk: int, world: int) -> int:
+    n = int(load().mb200_dist_symmetric_bytes(precision, tokens, hidden, topk, world))
+    if n < 0:
+        raise MB200Error("dist_symmetric_bytes: bad shape")
+    return n
+
+
+def dist_workspace_bytes(precision, tokens, hidden, intermediate, local_experts, topk, world) -> int:
+    n = int(load().mb200_dist_workspace_bytes(precision, tokens, hidden, intermediate, local_experts, topk, world))
+    if n < 0:
+        raise MB200Error(f"dist_workspace_bytes: {load().mb200_last_error().decode()}")
+    return n
+
+
+def peer_pointer_array(ptrs):
+    """ctypes ``void*[world]`` from a list of integer device addresses."""
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+def peer_barrier(ptr_array, rank: int, world: int, seq: int, status: Optional[torch.Tensor], device) -> None:
+    _check(load().mb200_peer_barrier(ptr_array, rank, world, seq, _ptr(status), _stream(device)), "peer_barrier")
+
+
+def dist_forward(precision, expert_parallel, x, w1, w2, w1_scale, w2_scale, topk_ids, topk_weights, expert_map,
+                 out, global_experts, rank, world, ptr_array, symmetric_bytes, seq_base, workspace):
+    """Enqueue one distributed layer forward (EP or TP) on the current stream."""
+    t, hidden = x.shape
+    e_local, two_n, _ = w1.shape
+    dev = x.device
+    _check(
+        load().mb200_dist_forward(
+            precision, 1 if expert_parallel else 0, _ptr(x), _ptr(w1), _ptr(w2), _ptr(w1_scale), _ptr(w2_scale),
+            _ptr(topk_ids), _ptr(topk_weights), _ptr(expert_map), _ptr(out), t, hidden, two_n // 2, e_local,
+            global_experts, topk_ids.shape[1], rank, world, ptr_array, symmetric_bytes, seq_base & 0xFFFFFFFF,
+            _ptr(workspace), workspace.numel(), dev.index or 0, _stream(dev),
+        ),
+        "dist_forward",
     )
 
 

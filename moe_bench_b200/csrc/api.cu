@@ -15,9 +15,10 @@ constexpr int kStageEvents = 6;
 thread_local cudaEvent_t g_stage_events[kStageEvents] = {};
 thread_local int g_stage_event_count = 0;
 
-inline void mark_stage(int i, cudaStream_t s) {
-  if (i < g_stage_event_count && g_stage_events[i]) cudaEventRecord(g_stage_events[i], s);
 }
+
+void mark_stage(int i, cudaStream_t s) {
+  if (i < g_stage_event_count && g_stage_events[i]) cudaEventRecord(g_stage_events[i], s);
 }
 
 void set_last_error(const char* fmt, ...) {
@@ -76,8 +77,6 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint6
 // ---------------------------------------------------------------------------
 // Workspace layout
 // ---------------------------------------------------------------------------
-namespace {
-
 int64_t row_capacity(int64_t tokens, int topk, int local_experts) {
   const int64_t a = tokens * topk;
   const int64_t touched = a < local_experts ? a : local_experts;
@@ -85,12 +84,10 @@ int64_t row_capacity(int64_t tokens, int topk, int local_experts) {
   return (rows + kTileM - 1) / kTileM * kTileM;
 }
 
-struct Layout {
-  int64_t status, counts, prefix, sorted, inverse, scratch, xg, act, y, total;
-  int64_t xs, acts;  // fp8 only: transposed activation scales [K/128][cap], [N/128][cap]
-};
-
+namespace {
 int64_t align_up(int64_t v) { return (v + 1023) / 1024 * 1024; }
+cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+}  // namespace
 
 Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk) {
   const int64_t eb = precision == MB200_PRECISION_FP8 ? 1 : 2;  // bytes per activation element
@@ -116,8 +113,6 @@ Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, 
   l.total = off;
   return l;
 }
-
-cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts, int topk) {
   MB200_REQUIRE(tokens >= 0 && topk >= 1 && local_experts >= 1, kInvalidArgument,
@@ -213,7 +208,6 @@ int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t 
   return launch_grouped_gemm_fp8(GemmMode(mode), map_a, map_b, g, device, stream);
 }
 
-}  // namespace
 }  // namespace mb200
 
 using namespace mb200;

@@ -1,0 +1,234 @@
+// Distributed layer forward: expert parallel (EP) and tensor parallel (TP) over
+// the GPUs of one NVLink box, one process per GPU.  Declared in
+// include/moe_bench_b200.h; replaces the AllGather -> fused_experts ->
+// ReduceScatter dataflow of the reference's serial scheme (schemes.py:117-143).
+//
+// Every rank owns a "symmetric" buffer of identical layout that all peers have
+// mapped (flags | routing | token payload | partial outputs).  One forward:
+//   1. stage: own routing and tokens into the symmetric buffer (EP/TP fp8:
+//      quantised to e4m3 + 1x128 scales first, so fp8 travels on the wire);
+//   2. barrier;
+//   3. routing of all ranks -> ring-ordered local copy; sort-and-pad against this
+//      rank's experts; dispatch = pull the needed rows from their owners;
+//   4. the two grouped GEMMs; the contributions of a token that landed on this
+//      rank are pre-reduced into one row of `partial`;
+//   5. barrier; the token's own rank pulls and sums the partial rows; barrier.
+
+#include "../../include/moe_bench_b200.h"
+#include <cstring>
+
+#include "layer.cuh"
+
+namespace mb200 {
+namespace {
+
+int64_t up1k(int64_t v) { return (v + 1023) / 1024 * 1024; }
+
+struct SymLayout {
+  int64_t flags, ids, weights, payload, payload_scales, partial, total;
+};
+
+SymLayout make_sym_layout(int precision, int64_t tokens, int hidden, int topk, int world) {
+  SymLayout l;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { int64_t o = off; off = up1k(off + bytes); return o; };
+  l.flags = take(1024);
+  l.ids = take(tokens * topk * 4);
+  l.weights = take(tokens * topk * 4);
+  l.payload = take(tokens * hidden * (precision == MB200_PRECISION_FP8 ? 1 : 2));
+  l.payload_scales = take(precision == MB200_PRECISION_FP8 ? tokens * (hidden / 128) * 4 : 0);
+  l.partial = take(int64_t(world) * tokens * hidden * 2);
+  l.total = off;
+  return l;
+}
+
+PeerTable offset_table(void* const* bases, int world, int64_t off) {
+  PeerTable t{};
+  for (int i = 0; i < world; ++i) t.ptr[i] = static_cast<char*>(bases[i]) + off;
+  return t;
+}
+
+}  // namespace
+}  // namespace mb200
+
+using namespace mb200;
+
+extern "C" {
+
+int64_t mb200_dist_symmetric_bytes(int precision, int64_t tokens, int hidden, int topk, int world) {
+  if (tokens < 0 || hidden <= 0 || topk < 1 || world < 1 || world > kMaxPeers) return -1;
+  return make_sym_layout(precision, tokens, hidden, topk, world).total;
+}
+
+int64_t mb200_dist_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
+                                   int local_experts, int topk, int world) {
+  if (world < 1 || world > kMaxPeers) return -1;
+  if (check_shape(tokens * world, hidden, intermediate, local_experts, topk)) return -1;
+  if (precision == MB200_PRECISION_FP8 && check_shape_fp8(hidden, intermediate)) return -1;
+  const Layout l = make_layout(precision, tokens * world, hidden, intermediate, local_experts, topk);
+  return l.total + 2 * up1k(tokens * world * topk * 4);
+}
+
+int mb200_peer_barrier(void* const* symmetric_ptrs, int rank, int world, uint32_t seq, int32_t* status,
+                       void* stream) {
+  MB200_REQUIRE(symmetric_ptrs && world >= 1 && world <= kMaxPeers, kInvalidArgument, "peer_barrier: bad argument");
+  return launch_peer_barrier(offset_table(symmetric_ptrs, world, 0), rank, world, seq, status,
+                             reinterpret_cast<cudaStream_t>(stream));
+}
+
+int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_states, const void* w1,
+                       const void* w2, const float* w1_scale, const float* w2_scale,
+                       const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
+                       void* out, int64_t tokens, int hidden, int intermediate, int local_experts,
+                       int global_experts, int topk, int rank, int world, void* const* symmetric_ptrs,
+                       int64_t symmetric_bytes, uint32_t seq_base, void* workspace, int64_t workspace_bytes,
+                       int device, void* stream) {
+  MB200_REQUIRE(precision == MB200_PRECISION_BF16 || precision == MB200_PRECISION_FP8, kInvalidArgument,
+                "dist_forward: unknown precision %d", precision);
+  MB200_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, kInvalidArgument,
+                "dist_forward: rank %d of %d (at most %d ranks)", rank, world, kMaxPeers);
+  const bool fp8 = precision == MB200_PRECISION_FP8;
+  const int64_t all_tokens = tokens * world;
+  int rc = check_shape(all_tokens, hidden, intermediate, local_experts, topk);
+  if (rc) return rc;
+  if (fp8 && (rc = check_shape_fp8(hidden, intermediate))) return rc;
+  MB200_REQUIRE(tokens > 0, kInvalidArgument, "dist_forward: every rank needs at least one token");
+  MB200_REQUIRE(hidden_states && w1 && w2 && topk_ids && topk_weights && out && workspace && symmetric_ptrs,
+                kInvalidArgument, "dist_forward: null pointer");
+  MB200_REQUIRE(!fp8 || (w1_scale && w2_scale), kInvalidArgument, "dist_forward: fp8 needs weight scales");
+  if (expert_parallel) {
+    MB200_REQUIRE(expert_map != nullptr, kInvalidArgument, "dist_forward: expert parallel needs expert_map");
+    MB200_REQUIRE(global_experts == local_experts * world, kInvalidArgument,
+                  "dist_forward: %d global experts != %d local x %d ranks", global_experts, local_experts, world);
+  }
+  const SymLayout sl = make_sym_layout(precision, tokens, hidden, topk, world);
+  MB200_REQUIRE(symmetric_bytes >= sl.total, kWorkspaceTooSmall, "dist_forward: symmetric buffer %lld < %lld bytes",
+                (long long)symmetric_bytes, (long long)sl.total);
+  const Layout l = make_layout(precision, all_tokens, hidden, intermediate, local_experts, topk);
+  const int64_t routing_bytes = up1k(all_tokens * topk * 4);
+  MB200_REQUIRE(workspace_bytes >= l.total + 2 * routing_bytes, kWorkspaceTooSmall,
+                "dist_forward: workspace %lld < %lld bytes", (long long)workspace_bytes,
+                (long long)(l.total + 2 * routing_bytes));
+  MB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, kInvalidArgument,
+                "dist_forward: workspace must be 1024-byte aligned");
+  for (int i = 0; i < world; ++i)
+    MB200_REQUIRE(symmetric_ptrs[i] && (reinterpret_cast<uintptr_t>(symmetric_ptrs[i]) & 1023) == 0, kInvalidArgument,
+                  "dist_forward: symmetric buffer of rank %d missing or not 1024-byte aligned", i);
+
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  char* ws = reinterpret_cast<char*>(workspace);
+  char* sym = static_cast<char*>(symmetric_ptrs[rank]);
+  int* status = reinterpret_cast<int*>(ws + l.status);
+  Schedule sched{reinterpret_cast<int*>(ws + l.counts), reinterpret_cast<int*>(ws + l.prefix),
+                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse)};
+  int* ids_all = reinterpret_cast<int*>(ws + l.total);
+  float* weights_all = reinterpret_cast<float*>(ws + l.total + routing_bytes);
+  const int64_t cap = row_capacity(all_tokens, topk, local_experts);
+  const PeerTable flags = offset_table(symmetric_ptrs, world, sl.flags);
+
+  // 1. stage own routing and tokens
+  mark_stage(0, s);
+  MB200_CHECK_CUDA(cudaMemcpyAsync(sym + sl.ids, topk_ids, tokens * topk * 4, cudaMemcpyDeviceToDevice, s));
+  MB200_CHECK_CUDA(cudaMemcpyAsync(sym + sl.weights, topk_weights, tokens * topk * 4, cudaMemcpyDeviceToDevice, s));
+  if (fp8) {
+    if ((rc = launch_group_quant_fp8(reinterpret_cast<const __nv_bfloat16*>(hidden_states), tokens, hidden,
+                                     reinterpret_cast<uint8_t*>(sym + sl.payload),
+                                     reinterpret_cast<float*>(sym + sl.payload_scales), hidden / 128, 0, s)))
+      return rc;
+  } else {
+    MB200_CHECK_CUDA(cudaMemcpyAsync(sym + sl.payload, hidden_states, tokens * int64_t(hidden) * 2,
+                                     cudaMemcpyDeviceToDevice, s));
+  }
+  // 2. every rank's staging is visible
+  if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 1, status, s))) return rc;
+  // 3. routing, schedule, dispatch
+  if ((rc = launch_gather_routing(offset_table(symmetric_ptrs, world, sl.ids),
+                                  offset_table(symmetric_ptrs, world, sl.weights), rank, world,
+                                  int(tokens * topk), ids_all, weights_all, s))) return rc;
+  if ((rc = launch_align(ids_all, all_tokens * topk, expert_parallel ? expert_map : nullptr, local_experts, sched,
+                         cap, reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
+  mark_stage(1, s);
+  if ((rc = launch_gather_rows_peer(fp8 ? 1 : 0, offset_table(symmetric_ptrs, world, sl.payload),
+                                    offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world, int(tokens),
+                                    topk, sched, local_experts, hidden, ws + l.xg,
+                                    fp8 ? reinterpret_cast<float*>(ws + l.xs) : nullptr, cap, s))) return rc;
+  mark_stage(2, s);
+  // 4. grouped GEMMs and the local pre-reduction into `partial`
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);
+  if (fp8) {
+    if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, ws + l.xg, reinterpret_cast<float*>(ws + l.xs), cap, w1, w1_scale,
+                                 local_experts, hidden, intermediate, sched.counts, sched.mtile_prefix,
+                                 sched.sorted_ids, nullptr, ws + l.act, reinterpret_cast<float*>(ws + l.acts), status,
+                                 device, s))) return rc;
+    mark_stage(3, s);
+    if ((rc = run_gemm_stage_fp8(kDownWeighted, ws + l.act, reinterpret_cast<float*>(ws + l.acts), cap, w2, w2_scale,
+                                 local_experts, hidden, intermediate, sched.counts, sched.mtile_prefix,
+                                 sched.sorted_ids, weights_all, y, nullptr, status, device, s))) return rc;
+  } else {
+    if ((rc = run_gemm_stage(kGateUpSwiglu, ws + l.xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
+                             sched.mtile_prefix, sched.sorted_ids, nullptr, ws + l.act, status, device, s))) return rc;
+    mark_stage(3, s);
+    if ((rc = run_gemm_stage(kDownWeighted, ws + l.act, cap, w2, local_experts, hidden, intermediate, sched.counts,
+                             sched.mtile_prefix, sched.sorted_ids, weights_all, y, status, device, s))) return rc;
+  }
+  mark_stage(4, s);
+  if ((rc = launch_combine_bf16(y, sched.inverse, int(all_tokens), topk, hidden,
+                                reinterpret_cast<__nv_bfloat16*>(sym + sl.partial), s))) return rc;
+  // 5. combine across ranks
+  if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 2, status, s))) return rc;
+  if ((rc = launch_reduce_partials(offset_table(symmetric_ptrs, world, sl.partial), rank, world, int(tokens), topk,
+                                   topk_ids, expert_parallel ? local_experts : 0, hidden,
+                                   reinterpret_cast<__nv_bfloat16*>(out), s))) return rc;
+  // peers may still be reading this rank's buffers: nobody restages before all are done
+  rc = launch_peer_barrier(flags, rank, world, seq_base + 3, status, s);
+  mark_stage(5, s);
+  return rc;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Set-up helpers: a buffer peers can map through CUDA IPC.  Used by the host
+// side when torch's symmetric-memory allocator is not available.  These are the
+// only entry points of the library that allocate; they are for setup()/close(),
+// never for the timed path.
+// ---------------------------------------------------------------------------
+extern "C" {
+
+int mb200_ipc_alloc(int64_t bytes, void** ptr_out, void* handle_out64) {
+  MB200_REQUIRE(bytes > 0 && ptr_out && handle_out64, kInvalidArgument, "ipc_alloc: bad argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  void* p = nullptr;
+  MB200_CHECK_CUDA(cudaMalloc(&p, size_t(bytes)));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    set_last_error("cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  MB200_CHECK_CUDA(cudaMemset(p, 0, size_t(bytes)));
+  memcpy(handle_out64, &h, sizeof(h));
+  *ptr_out = p;
+  return kOk;
+}
+
+int mb200_ipc_open(const void* handle64, void** ptr_out) {
+  MB200_REQUIRE(handle64 && ptr_out, kInvalidArgument, "ipc_open: bad argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  MB200_CHECK_CUDA(cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+  return kOk;
+}
+
+int mb200_ipc_close(void* ptr) {
+  MB200_CHECK_CUDA(cudaIpcCloseMemHandle(ptr));
+  return kOk;
+}
+
+int mb200_ipc_free(void* ptr) {
+  MB200_CHECK_CUDA(cudaFree(ptr));
+  return kOk;
+}
+
+}  // extern "C"

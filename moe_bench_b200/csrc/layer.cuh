@@ -84,6 +84,41 @@ struct GemmFp8Args {
 int launch_grouped_gemm_fp8(GemmMode mode, const CUtensorMap& map_a, const CUtensorMap& map_b,
                             const GemmFp8Args& args, int device, cudaStream_t stream);
 
+// ---- peer.cu: cross-GPU stages over peer-mapped memory -------------------------------------
+constexpr int kMaxPeers = 16;
+struct PeerTable {
+  void* ptr[kMaxPeers];  // one pointer per rank, valid in this process
+};
+int launch_peer_barrier(const PeerTable& flags, int rank, int world, uint32_t seq, int* status,
+                        cudaStream_t stream);
+int launch_gather_routing(const PeerTable& ids, const PeerTable& weights, int rank, int world,
+                          int per_rank, int* ids_all, float* weights_all, cudaStream_t stream);
+int launch_gather_rows_peer(int fp8, const PeerTable& x, const PeerTable& xs, int rank, int world,
+                            int tokens, int topk, const Schedule& sched, int local_experts, int hidden,
+                            void* out_rows, float* out_scales_t, int64_t row_capacity,
+                            cudaStream_t stream);
+int launch_reduce_partials(const PeerTable& partial, int rank, int world, int tokens, int topk,
+                           const int* topk_ids, int experts_per_rank, int hidden, __nv_bfloat16* out,
+                           cudaStream_t stream);
+
+// ---- api.cu helpers shared with dist.cu -----------------------------------------------------
+struct Layout {
+  int64_t status, counts, prefix, sorted, inverse, scratch, xg, act, y, total;
+  int64_t xs, acts;  // fp8 only: transposed activation scales [K/128][cap], [N/128][cap]
+};
+Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk);
+int64_t row_capacity(int64_t tokens, int topk, int local_experts);
+int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts, int topk);
+int check_shape_fp8(int hidden, int intermediate);
+int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
+                   int intermediate, const int* counts, const int* prefix, const int* sorted,
+                   const float* row_scale, void* out, int* status, int device, cudaStream_t stream);
+int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
+                       const float* w_scale, int local_experts, int hidden, int intermediate,
+                       const int* counts, const int* prefix, const int* sorted, const float* row_scale,
+                       void* out, float* out_scale_t, int* status, int device, cudaStream_t stream);
+void mark_stage(int i, cudaStream_t s);
+
 // ---- tensormap.cu ----------------------------------------------------------------------
 // Row-major 2-D tensor [rows][cols] of elem_bytes elements, boxes of
 // box_rows x (128 bytes of columns), 128-byte swizzle.

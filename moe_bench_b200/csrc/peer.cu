@@ -1,0 +1,230 @@
+// Cross-GPU stages of the distributed layer (one process per GPU, peers'
+// buffers mapped into this process: plain 64-bit pointers over NVLink).
+//
+// Data moves by P2P *loads* issued from these kernels (a rank pulls exactly the
+// rows it needs from the owning rank's buffer); the only remote *stores* are the
+// 4-byte barrier flags.  Nothing here waits inside a compute kernel: ranks meet
+// at the barrier kernel, whose spin is bounded.
+//
+//   peer_barrier      every rank writes a monotonic sequence number into its slot
+//                     of every peer's flag array (st.release.sys after a system
+//                     fence) and polls its own array (ld.acquire.sys), the
+//                     protocol of the reference's pcie_barrier_all
+//                     (kernels/tileoverlap/common/sm120_common.cuh:47-64), with a
+//                     time limit and a status word instead of an endless spin.
+//   gather_routing    all ranks' topk ids / weights -> one local array in ring
+//                     order (own rank first), replacing the two small
+//                     all-gathers of schemes.py:122-127 / tk_scheme.py:682-683.
+//   dispatch gathers  EP dispatch (replaces the all-gather of schemes.py:121):
+//                     the expert rank pulls the token rows routed to its experts
+//                     straight into its sorted, padded row buffer - e4m3 rows plus
+//                     their 1x128 scales (fp8 on the wire) or bf16 rows.
+//   reduce_partials   EP combine / TP output reduce (replaces the reduce-scatter
+//                     of schemes.py:142): every expert rank has pre-reduced the
+//                     contributions of a token that landed on it into one row;
+//                     the token's own rank pulls the <= W rows that exist and sums
+//                     them in fp32 in rank order.
+
+#include "layer.cuh"
+
+namespace mb200 {
+
+namespace {
+
+constexpr uint64_t kBarrierLimitNs = 3ull * 1000 * 1000 * 1000;
+
+__global__ void peer_barrier_kernel(PeerTable flags, int rank, int world, uint32_t seq, int* status) {
+  const int peer = threadIdx.x;
+  if (peer >= world) return;
+  // make this GPU's earlier writes visible system-wide before the flag
+  __threadfence_system();
+  uint32_t* remote = reinterpret_cast<uint32_t*>(flags.ptr[peer]) + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
+  const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.ptr[rank]) + peer;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (int32_t(v - seq) >= 0) break;  // monotonic, wrap-safe
+    if ((++spins & 0xFF) == 0) {
+      if (global_timer_ns() - t0 > kBarrierLimitNs) {
+        if (status) atomicCAS(status, 0, kDevWaitTimeout + 50 + peer);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __threadfence_system();
+}
+
+// ids_all[ring][t][j] = ids of rank (rank + ring) % world; same for weights.
+__global__ void gather_routing_kernel(PeerTable ids, PeerTable weights, int rank, int world,
+                                      int per_rank, int* __restrict__ ids_all,
+                                      float* __restrict__ weights_all) {
+  const int64_t total = int64_t(world) * per_rank;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int ring = int(i / per_rank);
+    const int off = int(i - int64_t(ring) * per_rank);
+    const int src = (rank + ring) % world;
+    ids_all[i] = reinterpret_cast<const int*>(ids.ptr[src])[off];
+    weights_all[i] = reinterpret_cast<const float*>(weights.ptr[src])[off];
+  }
+}
+
+// Sorted rows pulled from the source ranks.  n = (ring*T + t)*k + j.
+__global__ void gather_rows_peer_bf16_kernel(PeerTable x, int rank, int world, int tokens, int topk,
+                                             const int* __restrict__ sorted_ids,
+                                             const int* __restrict__ mtile_prefix, int local_experts,
+                                             int vec_per_row, uint4* __restrict__ xg, int64_t row_capacity) {
+  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * kTileM;
+  if (rows > row_capacity) rows = row_capacity;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int64_t row = int64_t(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += int64_t(gridDim.x) * warps_per_block) {
+    const int n = __ldg(sorted_ids + row);
+    if (n < 0) continue;
+    const int tok_global = n / topk;
+    const int ring = tok_global / tokens;
+    const int t = tok_global - ring * tokens;
+    const uint4* src = reinterpret_cast<const uint4*>(x.ptr[(rank + ring) % world]) + int64_t(t) * vec_per_row;
+    uint4* dst = xg + row * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) dst[v] = src[v];
+  }
+}
+
+// e4m3 rows + their scales ([T][K/128] at the source) -> sorted rows + group-major scales.
+__global__ void gather_rows_peer_fp8_kernel(PeerTable xq, PeerTable xs, int rank, int world, int tokens,
+                                            int topk, const int* __restrict__ sorted_ids,
+                                            const int* __restrict__ mtile_prefix, int local_experts,
+                                            int groups_per_row, uint4* __restrict__ out_q,
+                                            float* __restrict__ out_scales_t, int64_t row_capacity) {
+  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * kTileM;
+  if (rows > row_capacity) rows = row_capacity;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int vec_per_row = groups_per_row * 8;  // 128 bytes per group = 8 x 16 bytes
+  for (int64_t row = int64_t(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += int64_t(gridDim.x) * warps_per_block) {
+    const int n = __ldg(sorted_ids + row);
+    if (n < 0) continue;
+    const int tok_global = n / topk;
+    const int ring = tok_global / tokens;
+    const int t = tok_global - ring * tokens;
+    const int src_rank = (rank + ring) % world;
+    const uint4* src = reinterpret_cast<const uint4*>(xq.ptr[src_rank]) + int64_t(t) * vec_per_row;
+    const float* src_s = reinterpret_cast<const float*>(xs.ptr[src_rank]) + int64_t(t) * groups_per_row;
+    uint4* dst = out_q + row * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) dst[v] = src[v];
+    for (int g = lane; g < groups_per_row; g += 32) out_scales_t[int64_t(g) * row_capacity + row] = src_s[g];
+  }
+}
+
+__device__ __forceinline__ void add_bf16x8(const uint4& v, float (&acc)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+// out[t] = sum over ranks p (ascending) of partial_p[ring(p)*T + t], ring(p) =
+// (rank - p) mod world.  experts_per_rank > 0 (EP): only ranks that own one of
+// the token's experts are read; 0 (TP): every rank contributes.
+__global__ void reduce_partials_kernel(PeerTable partial, int rank, int world, int tokens, int topk,
+                                       const int* __restrict__ topk_ids, int experts_per_rank,
+                                       int vec_per_row, uint4* __restrict__ out) {
+  const int64_t total = int64_t(tokens) * vec_per_row;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int t = int(i / vec_per_row);
+    const int v = int(i - int64_t(t) * vec_per_row);
+    unsigned owners = 0xffffffffu;
+    if (experts_per_rank > 0) {
+      owners = 0;
+      for (int j = 0; j < topk; ++j) {
+        const int e = __ldg(topk_ids + int64_t(t) * topk + j);
+        if (e >= 0) owners |= 1u << (e / experts_per_rank);
+      }
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < world; ++p) {
+      if (!((owners >> p) & 1u)) continue;
+      const int ring = (rank - p + world) % world;
+      const uint4* src = reinterpret_cast<const uint4*>(partial.ptr[p]) +
+                         (int64_t(ring) * tokens + t) * vec_per_row + v;
+      add_bf16x8(*src, acc);
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+    out[i] = o;
+  }
+}
+
+int grid_for_rows(int64_t items, int threads, int waves) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int64_t blocks = (items + threads - 1) / threads;
+  const int64_t cap = int64_t(sms) * waves;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : int(blocks);
+}
+
+}  // namespace
+
+int launch_peer_barrier(const PeerTable& flags, int rank, int world, uint32_t seq, int* status,
+                        cudaStream_t stream) {
+  MB200_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, kInvalidArgument,
+                "peer_barrier: rank %d of %d (at most %d ranks)", rank, world, kMaxPeers);
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(flags, rank, world, seq, status);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_gather_routing(const PeerTable& ids, const PeerTable& weights, int rank, int world, int per_rank,
+                          int* ids_all, float* weights_all, cudaStream_t stream) {
+  const int threads = 256;
+  gather_routing_kernel<<<grid_for_rows(int64_t(world) * per_rank, threads, 4), threads, 0, stream>>>(
+      ids, weights, rank, world, per_rank, ids_all, weights_all);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_gather_rows_peer(int fp8, const PeerTable& x, const PeerTable& xs, int rank, int world, int tokens,
+                            int topk, const Schedule& sched, int local_experts, int hidden, void* out_rows,
+                            float* out_scales_t, int64_t row_capacity, cudaStream_t stream) {
+  const int threads = 256;
+  const int blocks = grid_for_rows(row_capacity * 32, threads, 16);
+  if (fp8) {
+    MB200_REQUIRE(hidden % 128 == 0, kUnsupportedShape, "dispatch: hidden=%d must be a multiple of 128", hidden);
+    gather_rows_peer_fp8_kernel<<<blocks, threads, 0, stream>>>(
+        x, xs, rank, world, tokens, topk, sched.sorted_ids, sched.mtile_prefix, local_experts, hidden / 128,
+        reinterpret_cast<uint4*>(out_rows), out_scales_t, row_capacity);
+  } else {
+    MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "dispatch: hidden=%d must be a multiple of 8", hidden);
+    gather_rows_peer_bf16_kernel<<<blocks, threads, 0, stream>>>(
+        x, rank, world, tokens, topk, sched.sorted_ids, sched.mtile_prefix, local_experts, hidden / 8,
+        reinterpret_cast<uint4*>(out_rows), row_capacity);
+  }
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_reduce_partials(const PeerTable& partial, int rank, int world, int tokens, int topk,
+                           const int* topk_ids, int experts_per_rank, int hidden, __nv_bfloat16* out,
+                           cudaStream_t stream) {
+  MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "reduce: hidden=%d must be a multiple of 8", hidden);
+  const int threads = 256;
+  reduce_partials_kernel<<<grid_for_rows(int64_t(tokens) * (hidden / 8), threads, 16), threads, 0, stream>>>(
+      partial, rank, world, tokens, topk, topk_ids, experts_per_rank, hidden / 8, reinterpret_cast<uint4*>(out));
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace mb200

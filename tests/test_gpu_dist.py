@@ -1,0 +1,124 @@
+"""The distributed scheme on GPUs: world size 1 in-process (the whole dispatch /
+GEMM / combine pipeline with this rank as its own peer), and world size 2 as
+two processes on two GPUs when the box has them.  Each rank is checked against
+the reference's distributed ground truth: reference_moe over its own token
+shard through the full logical model (reference distributed.py:64-84)."""
+
+import dataclasses
+import os
+import sys
+
+import pytest
+import torch
+
+from moe_bench_b200 import problem as P
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _to_dev(prob, dev):
+    def mv(t):
+        return None if t is None else t.to(dev)
+
+    qc = prob.quant_config
+    qc = None if qc is None else P.BlockQuantConfig(mv(qc.w1_scale), mv(qc.w2_scale), list(qc.block_shape))
+    return dataclasses.replace(
+        prob, hidden_states=mv(prob.hidden_states), w1=mv(prob.w1), w2=mv(prob.w2), topk_ids=mv(prob.topk_ids),
+        topk_weights=mv(prob.topk_weights), expert_map=mv(prob.expert_map), quant_config=qc,
+    )
+
+
+def _cfg(mode, precision, world, **kw):
+    base = dict(
+        hidden_size=512, intermediate_size=256 * world, num_experts=16, topk=4, parallel_mode=P.ParallelMode(mode),
+        world_size=world, precision=P.Precision(precision), distributed=True,
+        routing=P.RoutingConfig(distribution=P.Distribution.UNIFORM), seed=0, device="cpu",
+    )
+    base.update(kw)
+    return P.MoEBenchConfig(**base)
+
+
+@pytest.mark.parametrize("mode", ["ep", "tp"])
+@pytest.mark.parametrize("precision", ["bf16", "fp8"])
+@pytest.mark.parametrize("tokens", [1, 200])
+def test_scheme_world1(mode, precision, tokens):
+    from moe_bench_b200.scheme import DistContext, get_scheme
+
+    cfg = _cfg(mode, precision, 1)
+    prob = P.make_problem(cfg, tokens, 0)
+    ctx = DistContext(rank=0, world_size=1, local_rank=0, device=torch.device("cuda", 0))
+    scheme = get_scheme("b200")
+    scheme.setup(_to_dev(prob, "cuda:0"), ctx)
+    out = scheme.run().clone()
+    for _ in range(3):  # barrier sequence numbers keep growing across calls
+        again = scheme.run()
+    assert scheme.device_status() == 0
+    assert torch.equal(out, again)
+    res = O.verify_output(precision, out, O.reference_moe(P.make_golden_problem(cfg, tokens, 0)))
+    scheme.close()
+    assert res.passed and res.rel_err < 3e-2, (res.message, res.rel_err)
+
+
+def _rank_main(rank, world, port, mode, precision, tokens, dist_name, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+
+    from moe_bench_b200.scheme import DistContext, get_scheme
+
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("cpu:gloo,cuda:nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank,
+                            world_size=world, device_id=dev)
+    try:
+        cfg = _cfg(mode, precision, world, routing=P.RoutingConfig(distribution=P.Distribution(dist_name)))
+        prob = P.make_problem(cfg, tokens, rank)
+        ctx = DistContext(rank=rank, world_size=world, local_rank=rank, device=dev)
+        scheme = get_scheme("b200")
+        scheme.setup(_to_dev(prob, dev), ctx)
+        out = scheme.run().clone()
+        for _ in range(3):
+            again = scheme.run()
+        status = scheme.device_status()
+        same = bool(torch.equal(out, again))
+        res = O.verify_output(precision, out, O.reference_moe(P.make_golden_problem(cfg, tokens, rank)))
+        backend = scheme._buf.backend
+        scheme.close()
+        q.put((rank, status, same, res.passed, res.rel_err, res.message, backend))
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, -1, False, False, 1.0, traceback.format_exc()[-1500:], "error"))
+        raise exc
+    finally:
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize(
+    "mode,precision,tokens,dist_name",
+    [("ep", "fp8", 300, "uniform"), ("ep", "bf16", 64, "single"), ("tp", "bf16", 300, "uniform"),
+     ("tp", "fp8", 33, "skewed")],
+)
+def test_scheme_world2(mode, precision, tokens, dist_name):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    world = 2
+    port = 31000 + (os.getpid() + hash((mode, precision, tokens))) % 2000
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, mode, precision, tokens, dist_name, q))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=280) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, status, same, passed, rel, msg, backend in sorted(results):
+        assert status == 0, f"rank {rank}: device status {status} ({msg})"
+        assert same, f"rank {rank}: repeated runs differ"
+        assert passed and rel < 3e-2, f"rank {rank} [{backend}]: {msg} rel={rel}"
