@@ -17,9 +17,11 @@ latency; ``ms_per_step`` is that latency.  Prints ONE JSON line on rank 0.
 * ``cpu_baseline`` / ``--impl reference``: the CPU oracle (a port of the
                 reference's torch forward) on a bounded sample of the workload.
 
-With N > 1 every rank holds all experts and its own token shard (no exchange on
-the data path), so scaling is weak and the value is the sum over ranks divided
-by the slowest rank's time.
+With N > 1 the layer runs expert-parallel over the N GPUs (the reference's
+distributed EP mode): rank r owns 256/N experts and its own shard of T tokens,
+token dispatch and the weighted combine cross NVLink inside the library's
+kernels.  Per-GPU work is fixed (weak scaling); the value is the sum over ranks
+divided by the slowest rank's time.
 """
 
 from __future__ import annotations
@@ -172,13 +174,55 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line))
 
 
+class _LazyExperts:
+    """Indexable stand-in for a stacked ``[E, ...]`` weight tensor that builds
+    expert ``e`` when asked (the oracle only touches routed experts)."""
+
+    def __init__(self, count, make):
+        self.shape = (count,)
+        self._make = make
+
+    def __getitem__(self, e):
+        return self._make(int(e))
+
+
+def _lazy_logical_weights(cfg, P):
+    import torch
+
+    gen = torch.Generator(device=cfg.device)
+    cache = {}
+
+    def expert(e):
+        if e not in cache:
+            cache.clear()  # one expert at a time
+            w1, w2 = P._gen_expert_chunk(cfg, e, 0, gen)
+            if cfg.precision == P.Precision.FP8:
+                w1, s1 = P.per_block_cast_to_fp8(w1, cfg.block_shape)
+                w2, s2 = P.per_block_cast_to_fp8(w2, cfg.block_shape)
+                cache[e] = (w1, w2, s1, s2)
+            else:
+                cache[e] = (w1, w2, None, None)
+        return cache[e]
+
+    n = cfg.num_experts
+    w1 = _LazyExperts(n, lambda e: expert(e)[0])
+    w2 = _LazyExperts(n, lambda e: expert(e)[1])
+    qc = None
+    if cfg.precision == P.Precision.FP8:
+        qc = P.BlockQuantConfig(_LazyExperts(n, lambda e: expert(e)[2]), _LazyExperts(n, lambda e: expert(e)[3]),
+                                list(cfg.block_shape))
+    return w1, w2, qc
+
+
 def _config_dict(tokens: int, world: int, precision: str = "bf16"):
     wgb = 22.5 if precision == "bf16" else 11.3
     return {
         "workload": f"dsv32_{precision}_compute_only_T{tokens}" + ("" if EXPERTS == 256 else f"_E{EXPERTS}"),
         "tokens_per_gpu": tokens, "hidden": HIDDEN,
         "intermediate": INTER, "experts": EXPERTS, "topk": TOPK, "routing": "uniform", "seed": 0,
-        "parallelism": "single GPU" if world == 1 else f"{world} token-sharded replicas, all experts on every GPU",
+        "parallelism": "single GPU, all experts local" if world == 1 else
+                       f"ep{world}: {EXPERTS // world} experts and {tokens} own tokens per GPU, "
+                       "dispatch/combine by P2P pulls over NVLink",
         "l2": f"inputs larger than L2: {wgb} GB of expert weights are streamed every step",
     }
 
@@ -201,13 +245,29 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     tokens, steps, warmup = args.tokens, args.steps, args.warmup
     fp8 = args.precision == "fp8"
-    cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS,
-                                precision=P.Precision.FP8 if fp8 else P.Precision.BF16)
-    weights = P.make_weights(cfg)
-    x, ids, wts = P._gen_input(cfg, tokens, rank)  # every rank its own token shard
-    prob = P.MoEProblem(cfg, tokens, x, weights.w1, weights.w2, ids, wts, None, weights.quant_config)
-    impl = get_implementation("b200")
-    impl.setup(prob)
+    prec = P.Precision.FP8 if fp8 else P.Precision.BF16
+    if world == 1:
+        cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS, precision=prec)
+        weights = P.make_weights(cfg)
+        x, ids, wts = P._gen_input(cfg, tokens, 0)
+        prob = P.MoEProblem(cfg, tokens, x, weights.w1, weights.w2, ids, wts, None, weights.quant_config)
+        impl = get_implementation("b200")
+        impl.setup(prob)
+        run = lambda: impl.run(prob)  # noqa: E731
+        stage_names = capi.STAGE_NAMES
+    else:
+        # expert parallel over the N GPUs: rank r owns experts [r*E/N, (r+1)*E/N) and its own token shard
+        from moe_bench_b200.scheme import DistContext, get_scheme
+
+        cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS, precision=prec,
+                                    parallel_mode=P.ParallelMode.EP, world_size=world, distributed=True)
+        weights = P.make_weights(cfg, rank)
+        prob = P.make_problem(cfg, tokens, rank, weights=weights)
+        x, ids, wts = prob.hidden_states, prob.topk_ids, prob.topk_weights
+        impl = get_scheme("b200")
+        impl.setup(prob, DistContext(rank=rank, world_size=world, local_rank=local_rank, device=dev))
+        run = impl.run
+        stage_names = ("stage_routing_align", "dispatch", "gate_up_gemm", "down_gemm", "combine")
     assignments = tokens * TOPK
     flops_step = 6.0 * INTER * HIDDEN * assignments
 
@@ -224,7 +284,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         return float(t.item())
 
     for _ in range(warmup):
-        impl.run(prob)
+        run()
     # -------- device-resident timing, with per-stage events --------
     stage_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(steps)]
     for evs in stage_ev:
@@ -236,7 +296,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         start.record()
         for i in range(steps):
             capi.set_stage_events(stage_ev[i])
-            impl.run(prob)
+            run()
         end.record()
         torch.cuda.synchronize()
     capi.set_stage_events(None)
@@ -248,25 +308,24 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     if args.skip_extras:
         if rank == 0:
-            print(json.dumps({"ms_per_step": ms_step, "stage_ms": dict(zip(capi.STAGE_NAMES, stage_ms)),
+            print(json.dumps({"ms_per_step": ms_step, "stage_ms": dict(zip(stage_names, stage_ms)),
                               "config": _config_dict(tokens, world, args.precision),
                               "note": "profiling run, extras skipped"}))
         if world > 1:
+            impl.close()
             dist.destroy_process_group()
         return
 
     # -------- end to end: host buffers in, host buffer out --------
     hx, hi, hw = x.cpu().pin_memory(), ids.cpu().pin_memory(), wts.cpu().pin_memory()
     hout = torch.empty(tokens, HIDDEN, dtype=torch.bfloat16).pin_memory()
-    dx, di, dw = torch.empty_like(x), torch.empty_like(ids), torch.empty_like(wts)
-    prob_e2e = dataclasses.replace(prob, hidden_states=dx, topk_ids=di, topk_weights=dw)
 
     def e2e_step():
-        dx.copy_(hx, non_blocking=True)
-        di.copy_(hi, non_blocking=True)
-        dw.copy_(hw, non_blocking=True)
-        out = impl.run(prob_e2e)
-        hout.copy_(out, non_blocking=True)
+        # the step's inputs arrive from pinned host memory into the tensors the plugin reads
+        x.copy_(hx, non_blocking=True)
+        ids.copy_(hi, non_blocking=True)
+        wts.copy_(hw, non_blocking=True)
+        hout.copy_(run(), non_blocking=True)
 
     for _ in range(max(3, warmup // 2)):
         e2e_step()
@@ -283,10 +342,16 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     d2h = hout.numel() * 2
 
     # -------- parity spot check (outside any timed region) --------
-    out = impl.run(prob).clone()
+    out = run().clone()
     idx = torch.randperm(tokens, generator=torch.Generator().manual_seed(0))[: min(8, tokens)].to(dev)
-    sub = dataclasses.replace(prob, num_tokens=len(idx), hidden_states=x[idx].contiguous(),
-                              topk_ids=ids[idx].contiguous(), topk_weights=wts[idx].contiguous())
+    if world == 1:
+        ref_w1, ref_w2, ref_qc = weights.w1, weights.w2, weights.quant_config
+    else:
+        # ground truth of a distributed rank: its tokens through ALL experts (reference distributed.py:64-84);
+        # experts are generated on demand, only the ones the sampled tokens touch
+        ref_w1, ref_w2, ref_qc = _lazy_logical_weights(cfg, P)
+    sub = P.MoEProblem(cfg, len(idx), x[idx].contiguous(), ref_w1, ref_w2, ids[idx].contiguous(),
+                       wts[idx].contiguous(), None, ref_qc)
     check = O.verify_output(args.precision, out[idx], O.reference_moe(sub))
 
     if world > 1:
@@ -298,8 +363,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     if rank == 0:
         peaks = _peaks()
-        touched = _touched_experts(ids)
-        rows = assignments  # real rows; padding rows are neither loaded with data nor stored
+        # world == 1: experts this batch touches; EP: every local expert is hit, rows = this rank's share
+        touched = _touched_experts(ids) if world == 1 else EXPERTS // world
+        rows = assignments  # real rows (EP, uniform routing: the same number on average)
         wb = 1 if fp8 else 2  # bytes per weight / activation element on the GEMM's operands
         gemm_bytes = touched * 2 * INTER * HIDDEN * wb + rows * HIDDEN * wb + rows * INTER * wb
         gemm_flops = 4.0 * INTER * HIDDEN * assignments
@@ -322,7 +388,10 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         })
         layer_bytes = touched * 3 * INTER * HIDDEN * wb + 2 * tokens * HIDDEN * 2 + assignments * 8
         layer_roof_ms = max(layer_bytes / (peaks["hbm_gbs"] * 1e9), flops_step / (tc_peak * 1e12)) * 1e3
-        kernels_per_step = 7 if assignments > 16384 else 5
+        if world == 1:
+            kernels_per_step = 7 if assignments > 16384 else 5
+        else:  # 3 barriers, routing gather, align, dispatch, 2 GEMMs, partial combine, reduce (+ quantise)
+            kernels_per_step = 9 + (3 if assignments * world > 16384 else 1) + (1 if fp8 else 0)
         line = {
             "metric": METRIC, "value": flops_step * world / (ms_step * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
@@ -333,7 +402,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "gpu_launches": kernels_per_step * steps,
             "clocks": clocks.summary(),
             "roofline": roof,
-            "stage_ms": dict(zip(capi.STAGE_NAMES, stage_ms)),
+            "stage_ms": dict(zip(stage_names, stage_ms)),
             "layer_roofline_ms": layer_roof_ms, "layer_roofline_frac": layer_roof_ms / ms_step,
             "latency_us": ms_step * 1e3,
             "verify": "ok" if passed else "FAIL", "rel_err": check.rel_err,
@@ -343,6 +412,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
     if world > 1:
+        impl.close()
         dist.barrier()
         dist.destroy_process_group()
 
