@@ -305,6 +305,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     if impl.device_status() != 0:
         raise RuntimeError(f"device status {impl.device_status()}")
     stage_ms = [sum(evs[j].elapsed_time(evs[j + 1]) for evs in stage_ev) / steps for j in range(5)]
+    kernel_clocks = capi.read_kernel_clocks(impl._workspace)  # SM clock inside the GEMM kernels of the last step
 
     if args.skip_extras:
         if rank == 0:
@@ -400,7 +401,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "e2e": {"value": flops_step * world / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": kernels_per_step * steps,
-            "clocks": clocks.summary(),
+            "clocks": dict(clocks.summary(), in_kernel_sm_mhz=kernel_clocks),
             "roofline": roof,
             "stage_ms": dict(zip(stage_names, stage_ms)),
             "layer_roofline_ms": layer_roof_ms, "layer_roofline_frac": layer_roof_ms / ms_step,

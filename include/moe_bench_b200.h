@@ -32,10 +32,11 @@
 extern "C" {
 #endif
 
-#define MB200_ABI_VERSION 1
+#define MB200_ABI_VERSION 2
 #define MB200_PRECISION_BF16 0
 #define MB200_PRECISION_FP8 1
-#define MB200_TILE_M 128 /* expert segments are padded to this many rows */
+#define MB200_PAD_ROWS_BF16 16 /* bf16 forward: expert segments are padded to 16 rows */
+#define MB200_PAD_ROWS_FP8 128 /* fp8 forward: expert segments are padded to 128 rows */
 
 int mb200_abi_version(void);
 const char* mb200_last_error(void);
@@ -48,22 +49,24 @@ const char* mb200_last_error(void);
 int mb200_route_topk(const float* logits, int tokens, int experts, int topk, int32_t* topk_ids,
                      float* topk_weights, void* stream);
 
-/* Rows the sorted/padded assignment list can need: tokens*topk plus up to 127
- * padding rows per expert that can be hit, rounded up to MB200_TILE_M. */
-int64_t mb200_row_capacity(int64_t tokens, int topk, int local_experts);
+/* Rows the sorted/padded assignment list can need: tokens*topk plus up to
+ * pad_rows-1 padding rows per expert that can be hit, rounded up to pad_rows. */
+int64_t mb200_row_capacity(int64_t tokens, int topk, int local_experts, int pad_rows);
 int64_t mb200_align_scratch_bytes(int64_t tokens, int topk, int local_experts);
 
 /* Sort-and-pad of token->expert assignments (the moe_align_block_size step of
  * fused_experts, baseline.py:67; slot order of tk_scheme.py:98-126).
  * topk_ids [tokens, topk] int32 global ids; expert_map [global experts] int32
  * (global id -> local slot or -1) or NULL when every expert is local.
- * counts [E], mtile_prefix [E+1] (cumulative 128-row tiles; padded row offset of
- * expert e is 128*mtile_prefix[e]), sorted_ids [row_capacity] (flat assignment
+ * Every expert's segment is padded to a multiple of pad_rows rows
+ * (MB200_PAD_ROWS_BF16 / MB200_PAD_ROWS_FP8 for the two GEMM families).
+ * counts [E], mtile_prefix [E+1] (cumulative pad_rows-row blocks; padded row offset
+ * of expert e is pad_rows*mtile_prefix[e]), sorted_ids [row_capacity] (flat assignment
  * index token*topk+kpos per row, -1 for padding), inverse [tokens*topk] (row of
  * each assignment, -1 if its expert is not local). */
 int mb200_align(const int32_t* topk_ids, int64_t tokens, int topk, const int32_t* expert_map,
                 int local_experts, int32_t* counts, int32_t* mtile_prefix, int32_t* sorted_ids,
-                int32_t* inverse, int64_t row_capacity, void* scratch, void* stream);
+                int32_t* inverse, int64_t row_capacity, int pad_rows, void* scratch, void* stream);
 
 /* mb200_align for callers that cannot allocate device memory.  It has no
  * counterpart in the reference.
@@ -96,7 +99,7 @@ int mb200_align(const int32_t* topk_ids, int64_t tokens, int topk, const int32_t
 int mb200_align_noalloc(const int32_t* topk_ids, int64_t tokens, int topk,
                         const int32_t* expert_map, int local_experts, int32_t* counts,
                         int32_t* mtile_prefix, int32_t* sorted_ids, int32_t* inverse,
-                        int64_t row_capacity, void* stream);
+                        int64_t row_capacity, int pad_rows, void* stream);
 
 /* Dynamic activation quantisation, one fp32 scale per row per 128 elements
  * (reference.py:143-145 -> vLLM per_token_group_quant_fp8).
@@ -104,8 +107,8 @@ int mb200_align_noalloc(const int32_t* topk_ids, int64_t tokens, int topk,
 int mb200_group_quant_fp8(const void* x, int64_t rows, int hidden, void* q, float* scales,
                           void* stream);
 
-/* One grouped GEMM stage on an existing schedule (stage-level checks; the
- * forward entry points run both).  mode 0: act[row, 0:N] =
+/* One grouped GEMM stage on an existing schedule padded to MB200_PAD_ROWS_BF16
+ * (stage-level checks; the forward entry points run both).  mode 0: act[row, 0:N] =
  * SiLU(a.w1[e,0:N]) * (a.w1[e,N:2N]) for a [row_capacity, hidden] bf16 holding
  * the sorted rows, w1 [E, 2N, hidden], act [row_capacity, N] (reference.py:113-114).
  * mode 1: y[n, 0:hidden] = row_scale[n] * (a.w2[e]) for a [row_capacity, N],
@@ -135,7 +138,8 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
                            int intermediate, int local_experts, int topk, void* workspace,
                            int64_t workspace_bytes, int device, void* stream);
 
-/* fp8 counterpart of mb200_grouped_gemm_bf16 (reference.py:65-95 block matmul).
+/* fp8 counterpart of mb200_grouped_gemm_bf16 (reference.py:65-95 block matmul), on
+ * a schedule padded to MB200_PAD_ROWS_FP8.
  * a: e4m3 [row_capacity, K] sorted rows; a_scale_t: fp32 [K/128][row_capacity]
  * (group-major); w: e4m3 weights; w_scale: fp32 [E, rows/128, K/128].
  * mode 0 writes out = e4m3 [row_capacity, N] (SiLU(gate)*up rounded to bf16, then
@@ -212,6 +216,13 @@ int mb200_ipc_free(void* ptr);
  * (bench.py:52-101); this exists so one kernel's duration can be read inside a
  * timed region. */
 int mb200_set_stage_events(void* const* events, int count);
+
+/* The forward entry points also leave, in the first 256 bytes of the workspace
+ * (after the status word at byte 0), two pairs of uint64 at byte 32 and byte 48:
+ * {SM cycles, nanoseconds} that CTA 0 of the gate/up and of the down GEMM spent
+ * in the kernel during the last call; cycles/ns is the SM clock in GHz the kernel
+ * really ran at (a power-capped part runs tensor kernels far below the clock
+ * that the management library reports between kernels). */
 
 /* Copies the workspace status word to the host after synchronising `stream`
  * (0 = no kernel gave up a wait).  Not capturable. */

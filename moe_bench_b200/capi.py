@@ -18,7 +18,8 @@ LIB_PATH = os.path.join(_PKG, "libmoe_bench_b200.so")
 
 PRECISION_BF16 = 0
 PRECISION_FP8 = 1
-TILE_M = 128
+PAD_ROWS_BF16 = 16
+PAD_ROWS_FP8 = 128
 
 c_i32, c_i64, c_vp = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
 
@@ -27,10 +28,10 @@ SIGNATURES = {
     "mb200_abi_version": (c_i32, []),
     "mb200_last_error": (ctypes.c_char_p, []),
     "mb200_route_topk": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp]),
-    "mb200_row_capacity": (c_i64, [c_i64, c_i32, c_i32]),
+    "mb200_row_capacity": (c_i64, [c_i64, c_i32, c_i32, c_i32]),
     "mb200_align_scratch_bytes": (c_i64, [c_i64, c_i32, c_i32]),
-    "mb200_align": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
-    "mb200_align_noalloc": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp]),
+    "mb200_align": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp]),
+    "mb200_align_noalloc": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp]),
     "mb200_group_quant_fp8": (c_i32, [c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
     "mb200_grouped_gemm_bf16": (
         c_i32,
@@ -110,8 +111,8 @@ def _need(t: torch.Tensor, dtype, name: str) -> None:
         raise MB200Error(f"{name}: need a contiguous CUDA tensor of {dtype}, got {t.dtype} on {t.device}")
 
 
-def row_capacity(tokens: int, topk: int, local_experts: int) -> int:
-    return int(load().mb200_row_capacity(tokens, topk, local_experts))
+def row_capacity(tokens: int, topk: int, local_experts: int, pad_rows: int = PAD_ROWS_BF16) -> int:
+    return int(load().mb200_row_capacity(tokens, topk, local_experts, pad_rows))
 
 
 def workspace_bytes(precision: int, tokens: int, hidden: int, intermediate: int, local_experts: int, topk: int) -> int:
@@ -131,30 +132,32 @@ def route_topk(logits: torch.Tensor, topk: int):
     return ids, w
 
 
-def align(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], local_experts: int):
-    """Sort-and-pad; returns (counts[E], mtile_prefix[E+1], sorted_ids[cap], inverse[T*k])."""
+def align(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], local_experts: int,
+          pad_rows: int = PAD_ROWS_BF16):
+    """Sort-and-pad to ``pad_rows``; returns (counts[E], mtile_prefix[E+1], sorted_ids[cap], inverse[T*k])."""
     _need(topk_ids, torch.int32, "topk_ids")
     if expert_map is not None:
         _need(expert_map, torch.int32, "expert_map")
     t, k = topk_ids.shape
     dev = topk_ids.device
-    cap = row_capacity(t, k, local_experts)
+    cap = row_capacity(t, k, local_experts, pad_rows)
     counts = torch.empty(local_experts, dtype=torch.int32, device=dev)
     prefix = torch.empty(local_experts + 1, dtype=torch.int32, device=dev)
-    sorted_ids = torch.full((cap,), -2, dtype=torch.int32, device=dev)
+    sorted_ids = torch.full((max(cap, 1),), -2, dtype=torch.int32, device=dev)[:cap]
     inverse = torch.empty(max(t * k, 1), dtype=torch.int32, device=dev)
     scratch = torch.empty(load().mb200_align_scratch_bytes(t, k, local_experts), dtype=torch.uint8, device=dev)
     _check(
         load().mb200_align(
             _ptr(topk_ids), t, k, _ptr(expert_map), local_experts, _ptr(counts), _ptr(prefix),
-            _ptr(sorted_ids), _ptr(inverse), cap, _ptr(scratch), _stream(dev),
+            _ptr(sorted_ids), _ptr(inverse), cap, pad_rows, _ptr(scratch), _stream(dev),
         ),
         "align",
     )
     return counts, prefix, sorted_ids, inverse[: t * k]
 
 
-def align_noalloc(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], local_experts: int, outputs=None):
+def align_noalloc(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], local_experts: int, outputs=None,
+                  pad_rows: int = PAD_ROWS_BF16):
     """Sort-and-pad through the entry point that needs no scratch buffer.
 
     For hosts that may not allocate device memory while running (a server
@@ -171,7 +174,7 @@ def align_noalloc(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], lo
     t, k = topk_ids.shape
     dev = topk_ids.device
     if outputs is None:
-        cap = row_capacity(t, k, local_experts)
+        cap = row_capacity(t, k, local_experts, pad_rows)
         outputs = (
             torch.empty(local_experts, dtype=torch.int32, device=dev),
             torch.empty(local_experts + 1, dtype=torch.int32, device=dev),
@@ -182,7 +185,7 @@ def align_noalloc(topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor], lo
     _check(
         load().mb200_align_noalloc(
             _ptr(topk_ids), t, k, _ptr(expert_map), local_experts, _ptr(counts), _ptr(prefix),
-            _ptr(sorted_ids), _ptr(inverse), sorted_ids.shape[0], _stream(dev),
+            _ptr(sorted_ids), _ptr(inverse), sorted_ids.shape[0], pad_rows, _stream(dev),
         ),
         "align_noalloc",
     )
@@ -317,3 +320,14 @@ def set_stage_events(events) -> None:
         return
     arr = (ctypes.c_void_p * len(events))(*[ev.cuda_event for ev in events])
     _check(load().mb200_set_stage_events(arr, len(events)), "set_stage_events")
+
+
+def read_kernel_clocks(workspace: torch.Tensor) -> dict:
+    """SM clock (MHz) the two GEMM kernels of the last forward ran at, from the
+    cycle/nanosecond pairs the kernels leave in the workspace head.  Synchronises."""
+    torch.cuda.synchronize(workspace.device)
+    vals = workspace[32:64].view(torch.int64).cpu().tolist()
+    out = {}
+    for name, (cyc, ns) in (("gate_up_gemm", vals[0:2]), ("down_gemm", vals[2:4])):
+        out[name] = None if ns <= 0 else round(cyc / ns * 1e3, 1)
+    return out

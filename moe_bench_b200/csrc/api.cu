@@ -77,11 +77,11 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint6
 // ---------------------------------------------------------------------------
 // Workspace layout
 // ---------------------------------------------------------------------------
-int64_t row_capacity(int64_t tokens, int topk, int local_experts) {
+int64_t row_capacity(int64_t tokens, int topk, int local_experts, int pad_rows) {
   const int64_t a = tokens * topk;
   const int64_t touched = a < local_experts ? a : local_experts;
-  const int64_t rows = a + touched * (kTileM - 1);
-  return (rows + kTileM - 1) / kTileM * kTileM;
+  const int64_t rows = a + touched * (pad_rows - 1);
+  return (rows + pad_rows - 1) / pad_rows * pad_rows;
 }
 
 namespace {
@@ -92,7 +92,7 @@ cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk) {
   const int64_t eb = precision == MB200_PRECISION_FP8 ? 1 : 2;  // bytes per activation element
   const int64_t a = tokens * topk;
-  const int64_t cap = row_capacity(tokens, topk, local_experts);
+  const int64_t cap = row_capacity(tokens, topk, local_experts, pad_rows_of(precision));
   Layout l;
   int64_t off = 0;
   auto take = [&](int64_t bytes) { int64_t o = off; off = align_up(off + bytes); return o; };
@@ -128,9 +128,12 @@ int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts,
 
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
-                   const float* row_scale, void* out, int* status, int device, cudaStream_t stream) {
-  CUtensorMap map_a, map_b;
+                   const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
+                   unsigned long long* clock_probe) {
+  CUtensorMap map_w;
+  TokenMaps maps_t;
   GemmArgs g{};
+  g.clock_probe = clock_probe;
   g.counts = counts;
   g.mtile_prefix = prefix;
   g.sorted_ids = sorted;
@@ -139,24 +142,25 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
   g.out = out;
   g.status = status;
   int rc;
+  const int token_cols = mode == kGateUpSwiglu ? hidden : intermediate;
+  for (int i = 0; i < kTokenBoxes; ++i)
+    if ((rc = make_tensor_map_2d(&maps_t.m[i], a, 2, uint64_t(cap), uint64_t(token_cols), 16u << i))) return rc;
   if (mode == kGateUpSwiglu) {
-    if ((rc = make_tensor_map_2d(&map_a, a, 2, uint64_t(cap), uint64_t(hidden), kTileM))) return rc;
-    if ((rc = make_tensor_map_2d(&map_b, w, 2, uint64_t(local_experts) * 2 * intermediate, uint64_t(hidden), 128))) return rc;
+    if ((rc = make_tensor_map_2d(&map_w, w, 2, uint64_t(local_experts) * 2 * intermediate, uint64_t(hidden), 128))) return rc;
     g.n_tiles = (intermediate + 127) / 128;
     g.k_iters = (hidden + 63) / 64;
     g.b_rows_per_expert = 2 * intermediate;
     g.b_half_offset = intermediate;
     g.out_cols = intermediate;
   } else {
-    if ((rc = make_tensor_map_2d(&map_a, a, 2, uint64_t(cap), uint64_t(intermediate), kTileM))) return rc;
-    if ((rc = make_tensor_map_2d(&map_b, w, 2, uint64_t(local_experts) * hidden, uint64_t(intermediate), 256))) return rc;
+    if ((rc = make_tensor_map_2d(&map_w, w, 2, uint64_t(local_experts) * hidden, uint64_t(intermediate), 256))) return rc;
     g.n_tiles = (hidden + 255) / 256;
     g.k_iters = (intermediate + 63) / 64;
     g.b_rows_per_expert = hidden;
     g.b_half_offset = 0;
     g.out_cols = hidden;
   }
-  return launch_grouped_gemm_bf16(GemmMode(mode), map_a, map_b, g, device, stream);
+  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, device, stream);
 }
 
 int check_shape_fp8(int hidden, int intermediate) {
@@ -169,9 +173,11 @@ int check_shape_fp8(int hidden, int intermediate) {
 int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,
-                       void* out, float* out_scale_t, int* status, int device, cudaStream_t stream) {
+                       void* out, float* out_scale_t, int* status, int device, cudaStream_t stream,
+                       unsigned long long* clock_probe) {
   CUtensorMap map_a, map_b;
   GemmFp8Args g{};
+  g.clock_probe = clock_probe;
   g.counts = counts;
   g.mtile_prefix = prefix;
   g.sorted_ids = sorted;
@@ -225,8 +231,9 @@ int mb200_route_topk(const float* logits, int tokens, int experts, int topk, int
   return launch_route_topk(logits, tokens, experts, topk, topk_ids, topk_weights, as_stream(stream));
 }
 
-int64_t mb200_row_capacity(int64_t tokens, int topk, int local_experts) {
-  return row_capacity(tokens, topk, local_experts);
+int64_t mb200_row_capacity(int64_t tokens, int topk, int local_experts, int pad_rows) {
+  if (pad_rows < 1) return -1;
+  return row_capacity(tokens, topk, local_experts, pad_rows);
 }
 
 int64_t mb200_align_scratch_bytes(int64_t tokens, int topk, int local_experts) {
@@ -235,14 +242,15 @@ int64_t mb200_align_scratch_bytes(int64_t tokens, int topk, int local_experts) {
 
 int mb200_align(const int32_t* topk_ids, int64_t tokens, int topk, const int32_t* expert_map,
                 int local_experts, int32_t* counts, int32_t* mtile_prefix, int32_t* sorted_ids,
-                int32_t* inverse, int64_t row_cap, void* scratch, void* stream) {
+                int32_t* inverse, int64_t row_cap, int pad_rows, void* scratch, void* stream) {
   MB200_REQUIRE(tokens >= 0 && topk >= 1, kInvalidArgument, "align: tokens=%lld topk=%d", (long long)tokens, topk);
+  MB200_REQUIRE(pad_rows >= 1 && pad_rows <= 1024, kInvalidArgument, "align: pad_rows=%d (1..1024)", pad_rows);
   MB200_REQUIRE(counts && mtile_prefix && sorted_ids && scratch && (tokens == 0 || (topk_ids && inverse)),
                 kInvalidArgument, "align: null pointer");
-  MB200_REQUIRE(row_cap >= row_capacity(tokens, topk, local_experts), kWorkspaceTooSmall,
+  MB200_REQUIRE(row_cap >= row_capacity(tokens, topk, local_experts, pad_rows), kWorkspaceTooSmall,
                 "align: row capacity %lld < %lld", (long long)row_cap,
-                (long long)row_capacity(tokens, topk, local_experts));
-  Schedule s{counts, mtile_prefix, sorted_ids, inverse};
+                (long long)row_capacity(tokens, topk, local_experts, pad_rows));
+  Schedule s{counts, mtile_prefix, sorted_ids, inverse, pad_rows};
   return launch_align(topk_ids, tokens * topk, expert_map, local_experts, s, row_cap,
                       reinterpret_cast<int*>(scratch), as_stream(stream));
 }
@@ -260,8 +268,8 @@ int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_cap, const void
   MB200_REQUIRE(mode == 0 || mode == 1, kInvalidArgument, "grouped_gemm: mode=%d", mode);
   MB200_REQUIRE(a && w && counts && mtile_prefix && sorted_ids && out && (mode == 0 || row_scale),
                 kInvalidArgument, "grouped_gemm: null pointer");
-  MB200_REQUIRE(row_cap > 0 && row_cap % kTileM == 0, kInvalidArgument,
-                "grouped_gemm: row capacity %lld must be a positive multiple of %d", (long long)row_cap, kTileM);
+  MB200_REQUIRE(row_cap > 0 && row_cap % kPadBf16 == 0, kInvalidArgument,
+                "grouped_gemm: row capacity %lld must be a positive multiple of %d", (long long)row_cap, kPadBf16);
   int rc = check_shape(0, hidden, intermediate, local_experts, 1);
   if (rc) return rc;
   return run_gemm_stage(mode, a, row_cap, w, local_experts, hidden, intermediate, counts, mtile_prefix,
@@ -298,8 +306,8 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
   char* ws = reinterpret_cast<char*>(workspace);
   int* status = reinterpret_cast<int*>(ws + l.status);
   Schedule sched{reinterpret_cast<int*>(ws + l.counts), reinterpret_cast<int*>(ws + l.prefix),
-                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse)};
-  const int64_t cap = row_capacity(tokens, topk, local_experts);
+                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse), kPadBf16};
+  const int64_t cap = row_capacity(tokens, topk, local_experts, kPadBf16);
   __nv_bfloat16* xg = reinterpret_cast<__nv_bfloat16*>(ws + l.xg);
   __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(ws + l.act);
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);
@@ -312,10 +320,12 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
                                     topk, hidden, xg, cap, s))) return rc;
   mark_stage(2, s);
   if ((rc = run_gemm_stage(kGateUpSwiglu, xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
-                           sched.mtile_prefix, sched.sorted_ids, nullptr, act, status, device, s))) return rc;
+                           sched.mtile_prefix, sched.sorted_ids, nullptr, act, status, device, s,
+                             reinterpret_cast<unsigned long long*>(status + 8)))) return rc;
   mark_stage(3, s);
   if ((rc = run_gemm_stage(kDownWeighted, act, cap, w2, local_experts, hidden, intermediate, sched.counts,
-                           sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s))) return rc;
+                           sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s,
+                             reinterpret_cast<unsigned long long*>(status + 12)))) return rc;
   mark_stage(4, s);
   rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
   mark_stage(5, s);
@@ -361,8 +371,8 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
   char* ws = reinterpret_cast<char*>(workspace);
   int* status = reinterpret_cast<int*>(ws + l.status);
   Schedule sched{reinterpret_cast<int*>(ws + l.counts), reinterpret_cast<int*>(ws + l.prefix),
-                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse)};
-  const int64_t cap = row_capacity(tokens, topk, local_experts);
+                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse), kTileM};
+  const int64_t cap = row_capacity(tokens, topk, local_experts, kTileM);
   uint8_t* xq = reinterpret_cast<uint8_t*>(ws + l.xg);
   float* xs_t = reinterpret_cast<float*>(ws + l.xs);
   uint8_t* actq = reinterpret_cast<uint8_t*>(ws + l.act);
@@ -378,11 +388,13 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
   mark_stage(2, s);
   if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, xq, xs_t, cap, w1, w1_scale, local_experts, hidden, intermediate,
                                sched.counts, sched.mtile_prefix, sched.sorted_ids, nullptr, actq, acts_t, status,
-                               device, s))) return rc;
+                               device, s,
+                             reinterpret_cast<unsigned long long*>(status + 8)))) return rc;
   mark_stage(3, s);
   if ((rc = run_gemm_stage_fp8(kDownWeighted, actq, acts_t, cap, w2, w2_scale, local_experts, hidden, intermediate,
                                sched.counts, sched.mtile_prefix, sched.sorted_ids, topk_weights, y, nullptr, status,
-                               device, s))) return rc;
+                               device, s,
+                             reinterpret_cast<unsigned long long*>(status + 12)))) return rc;
   mark_stage(4, s);
   rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
   mark_stage(5, s);

@@ -120,10 +120,11 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   char* sym = static_cast<char*>(symmetric_ptrs[rank]);
   int* status = reinterpret_cast<int*>(ws + l.status);
   Schedule sched{reinterpret_cast<int*>(ws + l.counts), reinterpret_cast<int*>(ws + l.prefix),
-                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse)};
+                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse),
+                 pad_rows_of(precision)};
   int* ids_all = reinterpret_cast<int*>(ws + l.total);
   float* weights_all = reinterpret_cast<float*>(ws + l.total + routing_bytes);
-  const int64_t cap = row_capacity(all_tokens, topk, local_experts);
+  const int64_t cap = row_capacity(all_tokens, topk, local_experts, pad_rows_of(precision));
   const PeerTable flags = offset_table(symmetric_ptrs, world, sl.flags);
 
   // 1. stage own routing and tokens
@@ -159,17 +160,21 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
     if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, ws + l.xg, reinterpret_cast<float*>(ws + l.xs), cap, w1, w1_scale,
                                  local_experts, hidden, intermediate, sched.counts, sched.mtile_prefix,
                                  sched.sorted_ids, nullptr, ws + l.act, reinterpret_cast<float*>(ws + l.acts), status,
-                                 device, s))) return rc;
+                                 device, s,
+                             reinterpret_cast<unsigned long long*>(status + 8)))) return rc;
     mark_stage(3, s);
     if ((rc = run_gemm_stage_fp8(kDownWeighted, ws + l.act, reinterpret_cast<float*>(ws + l.acts), cap, w2, w2_scale,
                                  local_experts, hidden, intermediate, sched.counts, sched.mtile_prefix,
-                                 sched.sorted_ids, weights_all, y, nullptr, status, device, s))) return rc;
+                                 sched.sorted_ids, weights_all, y, nullptr, status, device, s,
+                             reinterpret_cast<unsigned long long*>(status + 12)))) return rc;
   } else {
     if ((rc = run_gemm_stage(kGateUpSwiglu, ws + l.xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
-                             sched.mtile_prefix, sched.sorted_ids, nullptr, ws + l.act, status, device, s))) return rc;
+                             sched.mtile_prefix, sched.sorted_ids, nullptr, ws + l.act, status, device, s,
+                             reinterpret_cast<unsigned long long*>(status + 8)))) return rc;
     mark_stage(3, s);
     if ((rc = run_gemm_stage(kDownWeighted, ws + l.act, cap, w2, local_experts, hidden, intermediate, sched.counts,
-                             sched.mtile_prefix, sched.sorted_ids, weights_all, y, status, device, s))) return rc;
+                             sched.mtile_prefix, sched.sorted_ids, weights_all, y, status, device, s,
+                             reinterpret_cast<unsigned long long*>(status + 12)))) return rc;
   }
   mark_stage(4, s);
   if ((rc = launch_combine_bf16(y, sched.inverse, int(all_tokens), topk, hidden,

@@ -7,15 +7,17 @@
 
 namespace mb200 {
 
-constexpr int kTileM = 128;        // rows per M tile; expert segments are padded to it
+constexpr int kTileM = 128;        // fp8 path: rows per M tile; expert segments are padded to it
+constexpr int kPadBf16 = 16;       // bf16 path: expert segments are padded to 16 rows
 constexpr int kMaxExperts = 1024;  // local experts per rank supported by the kernels
 
 // Output of the sort-and-pad step, all in device memory.
 struct Schedule {
   int* counts;        // [E]    real rows per local expert
-  int* mtile_prefix;  // [E+1]  cumulative M tiles; padded row offset = 128 * prefix
+  int* mtile_prefix;  // [E+1]  cumulative row blocks; padded row offset = pad_rows * prefix
   int* sorted_ids;    // [P]    flat assignment index (token*k + kpos) per row, -1 = padding
   int* inverse;       // [A]    row of each assignment, -1 = expert not on this rank
+  int pad_rows;       //        granule every expert segment is padded to
 };
 
 // ---- route_align.cu ---------------------------------------------------------------
@@ -44,10 +46,10 @@ int launch_gather_quant_fp8(const __nv_bfloat16* x, const Schedule& sched, int l
 // ---- grouped_gemm.cu -----------------------------------------------------------------
 struct GemmArgs {
   const int* counts;
-  const int* mtile_prefix;
+  const int* mtile_prefix;  // cumulative 16-row blocks
   const int* sorted_ids;
   int num_experts;
-  int n_tiles;            // output tiles per expert along the B rows
+  int n_tiles;            // feature blocks per expert (128 gate+up pairs, or 256 output rows)
   int k_iters;            // 128-byte K slices per tile
   int b_rows_per_expert;  // rows of the 2-D weight view per expert
   int b_half_offset;      // gate/up: row offset of the up half inside one expert
@@ -55,9 +57,16 @@ struct GemmArgs {
   void* out;
   const float* row_scale;  // per-assignment combine weight (second GEMM)
   int* status;
+  unsigned long long* clock_probe;  // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel
 };
 enum GemmMode : int { kGateUpSwiglu = 0, kDownWeighted = 1 };
-int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_a, const CUtensorMap& map_b,
+// Token-operand tensor maps with boxes of 16, 32, 64, 128 and 256 rows; the
+// kernel picks one from the largest expert segment it finds in the schedule.
+constexpr int kTokenBoxes = 5;
+struct TokenMaps {
+  CUtensorMap m[kTokenBoxes];
+};
+int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
                              const GemmArgs& args, int device, cudaStream_t stream);
 
 // grouped_gemm_fp8.cu: e4m3 operands, fp32 block scales applied in the epilogue
@@ -80,6 +89,7 @@ struct GemmFp8Args {
   float* out_scale_t;         // gate/up: [N/128][row_capacity]
   const float* row_scale;     // down: combine weights
   int* status;
+  unsigned long long* clock_probe;  // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel
 };
 int launch_grouped_gemm_fp8(GemmMode mode, const CUtensorMap& map_a, const CUtensorMap& map_b,
                             const GemmFp8Args& args, int device, cudaStream_t stream);
@@ -107,16 +117,19 @@ struct Layout {
   int64_t xs, acts;  // fp8 only: transposed activation scales [K/128][cap], [N/128][cap]
 };
 Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk);
-int64_t row_capacity(int64_t tokens, int topk, int local_experts);
+int64_t row_capacity(int64_t tokens, int topk, int local_experts, int pad_rows);
+inline int pad_rows_of(int precision) { return precision == 1 /* fp8 */ ? kTileM : kPadBf16; }
 int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts, int topk);
 int check_shape_fp8(int hidden, int intermediate);
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
-                   const float* row_scale, void* out, int* status, int device, cudaStream_t stream);
+                   const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
+                   unsigned long long* clock_probe = nullptr);
 int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,
-                       void* out, float* out_scale_t, int* status, int device, cudaStream_t stream);
+                       void* out, float* out_scale_t, int* status, int device, cudaStream_t stream,
+                       unsigned long long* clock_probe = nullptr);
 void mark_stage(int i, cudaStream_t s);
 
 // ---- tensormap.cu ----------------------------------------------------------------------

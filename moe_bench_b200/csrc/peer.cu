@@ -77,8 +77,9 @@ __global__ void gather_routing_kernel(PeerTable ids, PeerTable weights, int rank
 __global__ void gather_rows_peer_bf16_kernel(PeerTable x, int rank, int world, int tokens, int topk,
                                              const int* __restrict__ sorted_ids,
                                              const int* __restrict__ mtile_prefix, int local_experts,
-                                             int vec_per_row, uint4* __restrict__ xg, int64_t row_capacity) {
-  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * kTileM;
+                                             int vec_per_row, uint4* __restrict__ xg, int64_t row_capacity,
+                                             int pad) {
+  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * pad;
   if (rows > row_capacity) rows = row_capacity;
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -100,8 +101,8 @@ __global__ void gather_rows_peer_fp8_kernel(PeerTable xq, PeerTable xs, int rank
                                             int topk, const int* __restrict__ sorted_ids,
                                             const int* __restrict__ mtile_prefix, int local_experts,
                                             int groups_per_row, uint4* __restrict__ out_q,
-                                            float* __restrict__ out_scales_t, int64_t row_capacity) {
-  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * kTileM;
+                                            float* __restrict__ out_scales_t, int64_t row_capacity, int pad) {
+  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * pad;
   if (rows > row_capacity) rows = row_capacity;
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -205,12 +206,12 @@ int launch_gather_rows_peer(int fp8, const PeerTable& x, const PeerTable& xs, in
     MB200_REQUIRE(hidden % 128 == 0, kUnsupportedShape, "dispatch: hidden=%d must be a multiple of 128", hidden);
     gather_rows_peer_fp8_kernel<<<blocks, threads, 0, stream>>>(
         x, xs, rank, world, tokens, topk, sched.sorted_ids, sched.mtile_prefix, local_experts, hidden / 128,
-        reinterpret_cast<uint4*>(out_rows), out_scales_t, row_capacity);
+        reinterpret_cast<uint4*>(out_rows), out_scales_t, row_capacity, sched.pad_rows);
   } else {
     MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "dispatch: hidden=%d must be a multiple of 8", hidden);
     gather_rows_peer_bf16_kernel<<<blocks, threads, 0, stream>>>(
         x, rank, world, tokens, topk, sched.sorted_ids, sched.mtile_prefix, local_experts, hidden / 8,
-        reinterpret_cast<uint4*>(out_rows), row_capacity);
+        reinterpret_cast<uint4*>(out_rows), row_capacity, sched.pad_rows);
   }
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;

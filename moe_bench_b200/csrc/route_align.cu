@@ -159,7 +159,7 @@ __global__ void align_count_kernel(const int* __restrict__ topk_ids, const int* 
 // One block.  unit_hist[u][e] becomes the exclusive prefix over units; counts and
 // the cumulative M-tile table are written.
 __device__ void scan_units_and_experts(int* unit_hist, int units, int local_experts, int* counts,
-                                       int* mtile_prefix, int* smem_tiles /*[E+1]*/) {
+                                       int* mtile_prefix, int* smem_tiles /*[E+1]*/, int pad) {
   for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
     int run = 0;
     for (int u0 = 0; u0 < units; u0 += 8) {
@@ -174,7 +174,7 @@ __device__ void scan_units_and_experts(int* unit_hist, int units, int local_expe
       }
     }
     counts[e] = run;
-    smem_tiles[e] = (run + kTileM - 1) / kTileM;
+    smem_tiles[e] = (run + pad - 1) / pad;
   }
   __syncthreads();
   if (threadIdx.x < 32) {
@@ -202,17 +202,18 @@ __device__ void scan_units_and_experts(int* unit_hist, int units, int local_expe
 }
 
 __global__ void align_scan_kernel(int* unit_hist, int units, int local_experts, int* counts,
-                                  int* mtile_prefix) {
+                                  int* mtile_prefix, int pad) {
   extern __shared__ int tiles_smem[];
-  scan_units_and_experts(unit_hist, units, local_experts, counts, mtile_prefix, tiles_smem);
+  scan_units_and_experts(unit_hist, units, local_experts, counts, mtile_prefix, tiles_smem, pad);
 }
 
 // Mark the padding rows of expert e with -1; `lane`/`width` are the caller's
 // position in the group of threads that shares the expert.
 __device__ __forceinline__ void fill_padding(const int* counts, const int* mtile_prefix, int e,
-                                             int* sorted_ids, int64_t row_capacity, int lane, int width) {
-  const int64_t begin = int64_t(mtile_prefix[e]) * kTileM + counts[e];
-  int64_t end = int64_t(mtile_prefix[e + 1]) * kTileM;
+                                             int* sorted_ids, int64_t row_capacity, int lane, int width,
+                                             int pad) {
+  const int64_t begin = int64_t(mtile_prefix[e]) * pad + counts[e];
+  int64_t end = int64_t(mtile_prefix[e + 1]) * pad;
   if (end > row_capacity) end = row_capacity;
   for (int64_t p = begin + lane; p < end; p += width) sorted_ids[p] = -1;
 }
@@ -221,11 +222,11 @@ __global__ void align_scatter_kernel(const int* __restrict__ topk_ids, const int
                                      int64_t assignments, int local_experts, int64_t chunk, int units,
                                      const int* __restrict__ unit_base, const int* __restrict__ counts,
                                      const int* __restrict__ mtile_prefix, int* __restrict__ sorted_ids,
-                                     int* __restrict__ inverse, int64_t row_capacity) {
+                                     int* __restrict__ inverse, int64_t row_capacity, int pad) {
   extern __shared__ int hist_smem[];
   // one warp per expert, experts strided over every warp of the grid
   for (int e = blockIdx.x * kAlignWarps + (threadIdx.x >> 5); e < local_experts; e += gridDim.x * kAlignWarps)
-    fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity, threadIdx.x & 31, 32);
+    fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity, threadIdx.x & 31, 32, pad);
 
   const int warp = threadIdx.x >> 5;
   const int unit = blockIdx.x * kAlignWarps + warp;
@@ -239,7 +240,7 @@ __global__ void align_scatter_kernel(const int* __restrict__ topk_ids, const int
   walk_unit(topk_ids, expert_map, begin, end, assignments, local_experts, running,
             [&](int64_t n, int slot, int rank) {
               if (slot < 0) { inverse[n] = -1; return; }
-              const int64_t row = int64_t(mtile_prefix[slot]) * kTileM + base[slot] + rank;
+              const int64_t row = int64_t(mtile_prefix[slot]) * pad + base[slot] + rank;
               if (row < row_capacity) sorted_ids[row] = int(n);
               inverse[n] = int(row);
             });
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(kFusedWarps * 32)
 align_fused_kernel(const int* __restrict__ topk_ids, const int* __restrict__ expert_map,
                    int64_t assignments, int local_experts, int* __restrict__ counts,
                    int* __restrict__ mtile_prefix, int* __restrict__ sorted_ids,
-                   int* __restrict__ inverse, int64_t row_capacity, int* __restrict__ unit_hist) {
+                   int* __restrict__ inverse, int64_t row_capacity, int* __restrict__ unit_hist, int pad) {
   extern __shared__ int smem[];
   int* tiles_smem = smem;                              // [E+1]
   int* running_all = smem + (local_experts + 1);       // [32][E]
@@ -268,17 +269,17 @@ align_fused_kernel(const int* __restrict__ topk_ids, const int* __restrict__ exp
   for (int e = threadIdx.x & 31; e < local_experts; e += 32)
     unit_hist[size_t(warp) * local_experts + e] = running[e];
   __syncthreads();
-  scan_units_and_experts(unit_hist, kFusedWarps, local_experts, counts, mtile_prefix, tiles_smem);
+  scan_units_and_experts(unit_hist, kFusedWarps, local_experts, counts, mtile_prefix, tiles_smem, pad);
   __syncthreads();
   for (int e = warp; e < local_experts; e += kFusedWarps)
-    fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity, threadIdx.x & 31, 32);
+    fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity, threadIdx.x & 31, 32, pad);
   for (int e = threadIdx.x & 31; e < local_experts; e += 32) running[e] = 0;
   __syncwarp();
   const int* base = unit_hist + size_t(warp) * local_experts;
   walk_unit(topk_ids, expert_map, begin, end, assignments, local_experts, running,
             [&](int64_t n, int slot, int rank) {
               if (slot < 0) { inverse[n] = -1; return; }
-              const int64_t row = int64_t(mtile_prefix[slot]) * kTileM + base[slot] + rank;
+              const int64_t row = int64_t(mtile_prefix[slot]) * pad + base[slot] + rank;
               if (row < row_capacity) sorted_ids[row] = int(n);
               inverse[n] = int(row);
             });
@@ -312,11 +313,13 @@ int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map
                 "align: %d local experts, supported 1..%d", local_experts, kMaxExperts);
   MB200_REQUIRE(assignments >= 0 && assignments < (int64_t(1) << 31) - 4096, kUnsupportedShape,
                 "align: %lld assignments do not fit 32-bit row indices", (long long)assignments);
+  const int pad = sched.pad_rows;
+  MB200_REQUIRE(pad >= 1 && pad <= 1024, kInvalidArgument, "align: pad_rows=%d (1..1024)", pad);
   const size_t fused_smem = size_t(local_experts + 1 + kFusedWarps * local_experts) * sizeof(int);
   if (assignments <= kFusedMaxAssignments && fused_smem <= 48 * 1024) {
     align_fused_kernel<<<1, kFusedWarps * 32, fused_smem, stream>>>(
         topk_ids, expert_map, assignments, local_experts, sched.counts, sched.mtile_prefix,
-        sched.sorted_ids, sched.inverse, row_capacity, scratch);
+        sched.sorted_ids, sched.inverse, row_capacity, scratch, pad);
     MB200_CHECK_CUDA(cudaGetLastError());
     return kOk;
   }
@@ -330,12 +333,12 @@ int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map
     MB200_CHECK_CUDA(cudaGetLastError());
   }
   align_scan_kernel<<<1, 1024, size_t(local_experts + 1) * sizeof(int), stream>>>(
-      scratch, units, local_experts, sched.counts, sched.mtile_prefix);
+      scratch, units, local_experts, sched.counts, sched.mtile_prefix, pad);
   MB200_CHECK_CUDA(cudaGetLastError());
   const int sblocks = blocks > 0 ? blocks : 1;
   align_scatter_kernel<<<sblocks, kAlignThreads, hist_smem, stream>>>(
       topk_ids, expert_map, assignments, local_experts, chunk, units, scratch, sched.counts,
-      sched.mtile_prefix, sched.sorted_ids, sched.inverse, row_capacity);
+      sched.mtile_prefix, sched.sorted_ids, sched.inverse, row_capacity, pad);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
@@ -394,8 +397,9 @@ int noalloc_scratch(int** out) {
 extern "C" int mb200_align_noalloc(const int32_t* topk_ids, int64_t tokens, int topk,
                                    const int32_t* expert_map, int local_experts, int32_t* counts,
                                    int32_t* mtile_prefix, int32_t* sorted_ids, int32_t* inverse,
-                                   int64_t row_capacity, void* stream) {
+                                   int64_t row_capacity, int pad_rows, void* stream) {
   using namespace mb200;
+  MB200_REQUIRE(pad_rows >= 1 && pad_rows <= 1024, kInvalidArgument, "align_noalloc: pad_rows=%d", pad_rows);
   MB200_REQUIRE(tokens >= 0 && topk >= 1, kInvalidArgument, "align_noalloc: tokens=%lld topk=%d",
                 (long long)tokens, topk);
   MB200_REQUIRE(local_experts >= 1 && local_experts <= kNoAllocMaxExperts, kUnsupportedShape,
@@ -410,7 +414,7 @@ extern "C" int mb200_align_noalloc(const int32_t* topk_ids, int64_t tokens, int 
   MB200_REQUIRE(counts && mtile_prefix && sorted_ids && (tokens == 0 || (topk_ids && inverse)),
                 kInvalidArgument, "align_noalloc: null pointer");
   const int64_t touched = assignments < local_experts ? assignments : local_experts;
-  const int64_t need = (assignments + touched * (kTileM - 1) + kTileM - 1) / kTileM * kTileM;
+  const int64_t need = (assignments + touched * (pad_rows - 1) + pad_rows - 1) / pad_rows * pad_rows;
   MB200_REQUIRE(row_capacity >= need, kWorkspaceTooSmall, "align_noalloc: row capacity %lld < %lld",
                 (long long)row_capacity, (long long)need);
   int* scratch = nullptr;
@@ -418,7 +422,7 @@ extern "C" int mb200_align_noalloc(const int32_t* topk_ids, int64_t tokens, int 
   if (rc) return rc;
   // Every histogram entry a launch reads is written earlier by the same launch
   // sequence, so nothing left over from the previous call has to be cleared.
-  Schedule s{counts, mtile_prefix, sorted_ids, inverse};
+  Schedule s{counts, mtile_prefix, sorted_ids, inverse, pad_rows};
   return launch_align(topk_ids, assignments, expert_map, local_experts, s, row_capacity, scratch,
                       reinterpret_cast<cudaStream_t>(stream));
 }

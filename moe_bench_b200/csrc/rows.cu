@@ -19,8 +19,8 @@ namespace {
 __global__ void gather_rows_bf16_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted_ids,
                                         const int* __restrict__ mtile_prefix, int local_experts,
                                         int topk, int vec_per_row, uint4* __restrict__ xg,
-                                        int64_t row_capacity) {
-  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * kTileM;
+                                        int64_t row_capacity, int pad) {
+  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * pad;
   if (rows > row_capacity) rows = row_capacity;
   // one warp per row, rows strided over all warps of the grid
   const int warps_per_block = blockDim.x >> 5;
@@ -127,8 +127,8 @@ __global__ void group_quant_fp8_kernel(const uint4* __restrict__ x, int64_t rows
 __global__ void gather_quant_fp8_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted_ids,
                                         const int* __restrict__ mtile_prefix, int local_experts,
                                         int topk, int groups_per_row, uint2* __restrict__ xq,
-                                        float* __restrict__ scales_t, int64_t row_capacity) {
-  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * kTileM;
+                                        float* __restrict__ scales_t, int64_t row_capacity, int pad) {
+  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * pad;
   if (rows > row_capacity) rows = row_capacity;
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -183,7 +183,7 @@ int launch_gather_rows_bf16(const __nv_bfloat16* x, const Schedule& sched, int l
   const int blocks = grid_for(row_capacity * 32, threads, sm_count(), 16);
   gather_rows_bf16_kernel<<<blocks, threads, 0, stream>>>(
       reinterpret_cast<const uint4*>(x), sched.sorted_ids, sched.mtile_prefix, local_experts, topk,
-      hidden / 8, reinterpret_cast<uint4*>(xg), row_capacity);
+      hidden / 8, reinterpret_cast<uint4*>(xg), row_capacity, sched.pad_rows);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
@@ -221,7 +221,7 @@ int launch_gather_quant_fp8(const __nv_bfloat16* x, const Schedule& sched, int l
   const int blocks = grid_for(row_capacity * 32, threads, sm_count(), 16);
   gather_quant_fp8_kernel<<<blocks, threads, 0, stream>>>(
       reinterpret_cast<const uint4*>(x), sched.sorted_ids, sched.mtile_prefix, local_experts, topk,
-      hidden / 128, reinterpret_cast<uint2*>(xq), scales_t, row_capacity);
+      hidden / 128, reinterpret_cast<uint2*>(xq), scales_t, row_capacity, sched.pad_rows);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -35,11 +35,13 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 
 
 def test_abi_version_and_pure_host_queries(lib):
-    assert lib.mb200_abi_version() == 1
+    assert lib.mb200_abi_version() == 2
     # 8 assignments can hit at most 8 experts: 8 + 8*127 rows, rounded to 128
-    assert lib.mb200_row_capacity(1, 8, 256) == 1024
-    assert lib.mb200_row_capacity(8192, 8, 256) == (65536 + 256 * 127 + 127) // 128 * 128
-    assert lib.mb200_row_capacity(0, 8, 256) == 0
+    assert lib.mb200_row_capacity(1, 8, 256, 128) == 1024
+    assert lib.mb200_row_capacity(1, 8, 256, 16) == 128
+    assert lib.mb200_row_capacity(8192, 8, 256, 128) == (65536 + 256 * 127 + 127) // 128 * 128
+    assert lib.mb200_row_capacity(8192, 8, 256, 16) == (65536 + 256 * 15 + 15) // 16 * 16
+    assert lib.mb200_row_capacity(0, 8, 256, 16) == 0
     n = lib.mb200_workspace_bytes(capi.PRECISION_BF16, 128, 7168, 2048, 256, 8)
     assert n > 128 * 8 * 7168 * 2
     assert n % 1024 == 0
@@ -50,7 +52,7 @@ def test_argument_errors_are_reported_not_fatal(lib):
     assert b"hidden" in lib.mb200_last_error()
     rc = lib.mb200_route_topk(None, 4, 8, 9, None, None, None)
     assert rc != 0
-    rc = lib.mb200_align(None, 4, 2, None, 4096, None, None, None, None, 0, None, None)
+    rc = lib.mb200_align(None, 4, 2, None, 4096, None, None, None, None, 0, 16, None, None)
     assert rc != 0
 
 

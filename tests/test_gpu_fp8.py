@@ -46,7 +46,7 @@ def test_fp8_gemm_stages(tokens, hidden, inter, experts, topk, dist):
     prob = _fp8_problem(tokens, hidden, inter, experts, topk, dist)
     qc = prob.quant_config
     ids = prob.topk_ids
-    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, experts)
+    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, experts, capi.PAD_ROWS_FP8)
     cap = sorted_ids.shape[0]
     s_cpu = sorted_ids.cpu()
     rows = (s_cpu >= 0).nonzero().flatten()

@@ -42,8 +42,9 @@ ALIGN_CASES = [
 ]
 
 
+@pytest.mark.parametrize("pad", [16, 128])
 @pytest.mark.parametrize("dist,tokens,experts,topk,ep", ALIGN_CASES)
-def test_align_bit_exact(dist, tokens, experts, topk, ep):
+def test_align_bit_exact(dist, tokens, experts, topk, ep, pad):
     ids = _routing(dist, tokens, experts, topk)
     emap, local = None, experts
     if ep:
@@ -51,12 +52,12 @@ def test_align_bit_exact(dist, tokens, experts, topk, ep):
         emap = torch.full((experts,), -1, dtype=torch.int32)
         emap[3 * local : 4 * local] = torch.arange(local, dtype=torch.int32)
     counts, prefix, sorted_ids, inverse = capi.align(
-        ids.to(DEV), None if emap is None else emap.to(DEV), local
+        ids.to(DEV), None if emap is None else emap.to(DEV), local, pad
     )
     torch.cuda.synchronize()
-    o_counts, o_off, o_sorted, o_inv = O.align(ids.numpy(), None if emap is None else emap.numpy(), local)
+    o_counts, o_off, o_sorted, o_inv = O.align(ids.numpy(), None if emap is None else emap.numpy(), local, pad)
     assert np.array_equal(counts.cpu().numpy(), o_counts)
-    assert np.array_equal(prefix.cpu().numpy() * 128, o_off)
+    assert np.array_equal(prefix.cpu().numpy() * pad, o_off)
     rows = int(o_off[-1])
     assert np.array_equal(sorted_ids.cpu().numpy()[:rows], o_sorted)
     assert np.array_equal(inverse.cpu().numpy(), o_inv)
@@ -69,7 +70,7 @@ def test_align_is_a_permutation_at_full_size():
     assignment appears exactly once, inverse inverts sorted_ids, and rows are
     grouped by expert in ascending assignment order."""
     ids = _routing("uniform", 8192, 256, 8, seed=3)
-    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, 256)
+    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, 256, 16)
     s = sorted_ids.cpu().numpy()
     inv = inverse.cpu().numpy()
     real = s[s >= 0]
@@ -78,7 +79,7 @@ def test_align_is_a_permutation_at_full_size():
     flat = ids.numpy().reshape(-1)
     pre = prefix.cpu().numpy()
     for e in (0, 17, 255):
-        seg = s[pre[e] * 128 : pre[e + 1] * 128]
+        seg = s[pre[e] * 16 : pre[e + 1] * 16]
         seg = seg[seg >= 0]
         assert np.all(flat[seg] == e) and np.all(np.diff(seg) > 0)
 
@@ -134,13 +135,15 @@ def _stage_problem(tokens, hidden, inter, experts, topk, dist="uniform", seed=0)
         (300, 512, 256, 4, 2, "uniform"),    # several M tiles per expert, ragged last tile
         (40, 1024, 384, 16, 4, "single"),    # empty experts
         (200, 192, 320, 8, 2, "uniform"),    # hidden/intermediate not multiples of the tile width
+        (2000, 256, 128, 4, 2, "uniform"),   # ~1000 rows per expert: several 256-token blocks, balanced split
+        (37, 512, 256, 32, 1, "uniform"),    # one or two rows per expert: 16-token boxes
     ],
 )
 def test_grouped_gemm_stages(tokens, hidden, inter, experts, topk, dist):
     """Gate/up + SiLU-mul and down + weight stages against fp32 matmuls on the CPU."""
     prob = _stage_problem(tokens, hidden, inter, experts, topk, dist)
     ids = prob.topk_ids
-    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, experts)
+    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, experts, capi.PAD_ROWS_BF16)
     cap = sorted_ids.shape[0]
     s_cpu = sorted_ids.cpu()
     x = prob.hidden_states

@@ -54,9 +54,10 @@ def test_noalloc_align_matches_align_on_consecutive_calls():
             local = experts // ep
             emap = torch.full((experts,), -1, dtype=torch.int32, device=DEV)
             emap[5 * local : 6 * local] = torch.arange(local, dtype=torch.int32, device=DEV)
-        want = capi.align(ids, emap, local)
+        pad = (16, 128)[i % 2]  # both padding granules the library uses
+        want = capi.align(ids, emap, local, pad)
         # preallocated outputs: from here on the call itself allocates nothing
-        cap = capi.row_capacity(tokens, topk, local)
+        cap = capi.row_capacity(tokens, topk, local, pad)
         outs = (
             torch.empty(local, dtype=torch.int32, device=DEV),
             torch.empty(local + 1, dtype=torch.int32, device=DEV),
@@ -66,12 +67,12 @@ def test_noalloc_align_matches_align_on_consecutive_calls():
         outs2 = tuple(t.clone() for t in outs)
         if i == 0:
             # first call on the device: looks up the built-in array's address
-            capi.align_noalloc(ids, emap, local, outputs=tuple(t.clone() for t in outs))
+            capi.align_noalloc(ids, emap, local, outputs=tuple(t.clone() for t in outs), pad_rows=pad)
         torch.cuda.synchronize()
         held_by_torch = torch.cuda.memory_allocated()
         free_before = torch.cuda.mem_get_info()[0]
-        got = capi.align_noalloc(ids, emap, local, outputs=outs)
-        got_again = capi.align_noalloc(ids, emap, local, outputs=outs2)
+        got = capi.align_noalloc(ids, emap, local, outputs=outs, pad_rows=pad)
+        got_again = capi.align_noalloc(ids, emap, local, outputs=outs2, pad_rows=pad)
         torch.cuda.synchronize()
         # neither torch nor the library took device memory during the two calls
         assert torch.cuda.memory_allocated() == held_by_torch
@@ -89,10 +90,10 @@ def test_noalloc_align_refuses_oversized_problems():
     p = ids.data_ptr()
     o = out.data_ptr()
     # too many local experts
-    rc = lib.mb200_align_noalloc(p, 4, 2, None, 257, o, o, o, o, 4096, None)
+    rc = lib.mb200_align_noalloc(p, 4, 2, None, 257, o, o, o, o, 4096, 16, None)
     assert rc == 5 and b"at most 256" in lib.mb200_last_error()
     # too many assignments (nothing is launched, so the pointers are never used)
-    rc = lib.mb200_align_noalloc(p, (1 << 20) // 2 + 1, 2, None, 8, o, o, o, o, 1 << 30, None)
+    rc = lib.mb200_align_noalloc(p, (1 << 20) // 2 + 1, 2, None, 8, o, o, o, o, 1 << 30, 16, None)
     assert rc == 5 and b"mb200_align" in lib.mb200_last_error()
     with pytest.raises(capi.MB200Error):
         capi.align_noalloc(torch.zeros(4, 2, dtype=torch.int32, device=DEV), None, 300)
