@@ -214,6 +214,47 @@ def _lazy_logical_weights(cfg, P):
     return w1, w2, qc
 
 
+def _time_vllm_baseline(prob, world, dev, flops_step, barrier, max_over_ranks, ours):
+    """vLLM's Triton fused_experts (N=1) or the reference's serial scheme
+    all-gather -> fused_experts -> reduce-scatter (N>1), timed like the main arm.
+    A baseline, not an optimisation target; any failure is reported, not fatal."""
+    import torch
+    import torch.distributed as dist
+
+    from moe_bench_b200 import baselines as B
+
+    try:
+        run = B.vllm_compute_only(prob) if world == 1 else B.vllm_serial_scheme(prob, world)
+        for _ in range(3):
+            res = run()
+        barrier()
+        n = 5
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            res = run()
+        e.record()
+        torch.cuda.synchronize()
+        ms = max_over_ranks(s.elapsed_time(e) / n)
+        diff = float((res.float() - ours.float()).norm() / ours.float().norm().clamp_min(1e-12))
+        ok = 1.0
+    except Exception as exc:  # noqa: BLE001
+        ms, diff, ok, reason = 0.0, 0.0, 0.0, f"{type(exc).__name__}: {str(exc)[:200]}"
+    if world > 1:  # every rank must agree on success before rank 0 reports
+        flag = torch.tensor([ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if flag.item() == 0 and ok:
+            ok, reason = 0.0, "failed on another rank"
+    if not ok:
+        return {"unavailable": reason}
+    return {
+        "impl": "vLLM fused_experts (Triton)" if world == 1 else
+                "all_gather + vLLM fused_experts + reduce_scatter (reference serial scheme)",
+        "ms_per_step": ms, "value": flops_step * world / (ms * 1e-3) / 1e12, "unit": UNIT,
+        "rel_diff_vs_b200": diff,
+    }
+
+
 def _config_dict(tokens: int, world: int, precision: str = "bf16"):
     wgb = 22.5 if precision == "bf16" else 11.3
     return {
@@ -355,6 +396,10 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                        wts[idx].contiguous(), None, ref_qc)
     check = O.verify_output(args.precision, out[idx], O.reference_moe(sub))
 
+    # -------- reported GPU baseline: the reference's own vLLM path on the same box --------
+    gpu_base = {"unavailable": "skipped (--no-gpu-baseline)"}
+    if not args.no_gpu_baseline:
+        gpu_base = _time_vllm_baseline(prob, world, dev, flops_step, barrier, max_over_ranks, out)
     if world > 1:
         ok = torch.tensor([1.0 if check.passed else 0.0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
@@ -408,6 +453,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "latency_us": ms_step * 1e3,
             "verify": "ok" if passed else "FAIL", "rel_err": check.rel_err,
         }
+        line["gpu_baseline"] = gpu_base
         if world == 1 and not args.no_cpu_baseline and not fp8:  # the CPU leg times the bf16 oracle
             res = _time_cpu_oracle(tokens, 20, 2)
             line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -428,6 +474,7 @@ def main() -> None:
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8"],
                     help="bf16 = the headline workload; fp8 = the block-quantised config of the same shape")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-baseline", action="store_true", help="skip the vLLM fused_experts baseline leg")
     ap.add_argument("--experts", type=int, default=256, help="expert count (lower it only to size a profiler capture)")
     ap.add_argument("--skip-extras", action="store_true", help="timed region only: no e2e, parity or CPU legs")
     args = ap.parse_args()
