@@ -166,7 +166,7 @@ def run_reference(args, rank: int, world: int) -> None:
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": res["passes"], "warmup": min(args.warmup, 3), "ms_per_step": res["ms_per_pass"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": _config_dict(args.tokens, world),
+        "config": _config_dict(args.tokens, world, "bf16", args.mode, args.distribution),
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -192,10 +192,18 @@ def _lazy_logical_weights(cfg, P):
     gen = torch.Generator(device=cfg.device)
     cache = {}
 
+    tp = cfg.parallel_mode == P.ParallelMode.TP
+    shards = range(cfg.world_size) if tp else (0,)
+
     def expert(e):
         if e not in cache:
             cache.clear()  # one expert at a time
-            w1, w2 = P._gen_expert_chunk(cfg, e, 0, gen)
+            # the logical expert: TP concatenates the shards' gate rows, then their up rows, and
+            # the w2 column blocks (reference data.py:340-357)
+            chunks = [P._gen_expert_chunk(cfg, e, s, gen) for s in shards]
+            halves = [c[0].chunk(2, dim=0) for c in chunks]
+            w1 = torch.cat([h[0] for h in halves] + [h[1] for h in halves], dim=0)
+            w2 = torch.cat([c[1] for c in chunks], dim=1)
             if cfg.precision == P.Precision.FP8:
                 w1, s1 = P.per_block_cast_to_fp8(w1, cfg.block_shape)
                 w2, s2 = P.per_block_cast_to_fp8(w2, cfg.block_shape)
@@ -255,15 +263,17 @@ def _time_vllm_baseline(prob, world, dev, flops_step, barrier, max_over_ranks, o
     }
 
 
-def _config_dict(tokens: int, world: int, precision: str = "bf16"):
+def _config_dict(tokens: int, world: int, precision: str = "bf16", mode: str = "ep", distribution: str = "uniform"):
     wgb = 22.5 if precision == "bf16" else 11.3
     return {
         "workload": f"dsv32_{precision}_compute_only_T{tokens}" + ("" if EXPERTS == 256 else f"_E{EXPERTS}"),
         "tokens_per_gpu": tokens, "hidden": HIDDEN,
-        "intermediate": INTER, "experts": EXPERTS, "topk": TOPK, "routing": "uniform", "seed": 0,
+        "intermediate": INTER, "experts": EXPERTS, "topk": TOPK, "routing": distribution, "seed": 0,
         "parallelism": "single GPU, all experts local" if world == 1 else
-                       f"ep{world}: {EXPERTS // world} experts and {tokens} own tokens per GPU, "
-                       "dispatch/combine by P2P pulls over NVLink",
+                       (f"ep{world}: {EXPERTS // world} experts and {tokens} own tokens per GPU, "
+                        "dispatch/combine by P2P pulls over NVLink" if mode == "ep" else
+                        f"tp{world}: all experts, intermediate/{world} columns and {tokens} own tokens per GPU, "
+                        "token gather and output reduce by P2P pulls over NVLink"),
         "l2": f"inputs larger than L2: {wgb} GB of expert weights are streamed every step",
     }
 
@@ -288,7 +298,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     fp8 = args.precision == "fp8"
     prec = P.Precision.FP8 if fp8 else P.Precision.BF16
     if world == 1:
-        cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS, precision=prec)
+        cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS, precision=prec,
+                                    routing=P.RoutingConfig(distribution=P.Distribution(args.distribution)))
         weights = P.make_weights(cfg)
         x, ids, wts = P._gen_input(cfg, tokens, 0)
         prob = P.MoEProblem(cfg, tokens, x, weights.w1, weights.w2, ids, wts, None, weights.quant_config)
@@ -301,7 +312,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         from moe_bench_b200.scheme import DistContext, get_scheme
 
         cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS, precision=prec,
-                                    parallel_mode=P.ParallelMode.EP, world_size=world, distributed=True)
+                                    parallel_mode=P.ParallelMode(args.mode), world_size=world, distributed=True,
+                                    routing=P.RoutingConfig(distribution=P.Distribution(args.distribution)))
         weights = P.make_weights(cfg, rank)
         prob = P.make_problem(cfg, tokens, rank, weights=weights)
         x, ids, wts = prob.hidden_states, prob.topk_ids, prob.topk_weights
@@ -310,6 +322,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         run = impl.run
         stage_names = ("stage_routing_align", "dispatch", "gate_up_gemm", "down_gemm", "combine")
     assignments = tokens * TOPK
+    # TP: every rank computes all W*T*k assignments on intermediate/W columns = the same flops per rank
     flops_step = 6.0 * INTER * HIDDEN * assignments
 
     def barrier():
@@ -351,7 +364,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     if args.skip_extras:
         if rank == 0:
             print(json.dumps({"ms_per_step": ms_step, "stage_ms": dict(zip(stage_names, stage_ms)),
-                              "config": _config_dict(tokens, world, args.precision),
+                              "config": _config_dict(tokens, world, args.precision, args.mode, args.distribution),
                               "note": "profiling run, extras skipped"}))
         if world > 1:
             impl.close()
@@ -410,10 +423,15 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     if rank == 0:
         peaks = _peaks()
         # world == 1: experts this batch touches; EP: every local expert is hit, rows = this rank's share
-        touched = _touched_experts(ids) if world == 1 else EXPERTS // world
-        rows = assignments  # real rows (EP, uniform routing: the same number on average)
+        tp = world > 1 and args.mode == "tp"
+        if world == 1:
+            touched, rows, n_local = _touched_experts(ids), assignments, INTER
+        elif tp:   # all experts, intermediate/W columns, every rank computes all W*T tokens
+            touched, rows, n_local = EXPERTS, assignments * world, INTER // world
+        else:      # EP, uniform routing: every local expert is hit, rows = this rank's share on average
+            touched, rows, n_local = EXPERTS // world, assignments, INTER
         wb = 1 if fp8 else 2  # bytes per weight / activation element on the GEMM's operands
-        gemm_bytes = touched * 2 * INTER * HIDDEN * wb + rows * HIDDEN * wb + rows * INTER * wb
+        gemm_bytes = touched * 2 * n_local * HIDDEN * wb + rows * HIDDEN * wb + rows * n_local * wb
         gemm_flops = 4.0 * INTER * HIDDEN * assignments
         gemm_ms = stage_ms[2]
         t_hbm = gemm_bytes / (peaks["hbm_gbs"] * 1e9)
@@ -432,7 +450,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "peak_source": peaks["source"] + " (burst)", "algorithmic_bytes": gemm_bytes,
             "algorithmic_flops": gemm_flops, "t_hbm_ms": t_hbm * 1e3, "t_tensor_ms": t_tc * 1e3,
         })
-        layer_bytes = touched * 3 * INTER * HIDDEN * wb + 2 * tokens * HIDDEN * 2 + assignments * 8
+        layer_bytes = touched * 3 * n_local * HIDDEN * wb + 2 * tokens * HIDDEN * 2 + assignments * 8
         layer_roof_ms = max(layer_bytes / (peaks["hbm_gbs"] * 1e9), flops_step / (tc_peak * 1e12)) * 1e3
         if world == 1:
             kernels_per_step = 7 if assignments > 16384 else 5
@@ -442,7 +460,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "metric": METRIC, "value": flops_step * world / (ms_step * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.precision,
-            "data": "synthetic", "config": _config_dict(tokens, world, args.precision),
+            "data": "synthetic", "config": _config_dict(tokens, world, args.precision, args.mode, args.distribution),
             "e2e": {"value": flops_step * world / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": kernels_per_step * steps,
@@ -473,6 +491,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8"],
                     help="bf16 = the headline workload; fp8 = the block-quantised config of the same shape")
+    ap.add_argument("--mode", default="ep", choices=["ep", "tp"], help="parallel mode when --gpus > 1")
+    ap.add_argument("--distribution", default="uniform", choices=["uniform", "single", "skewed", "balanced"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true", help="skip the vLLM fused_experts baseline leg")
     ap.add_argument("--experts", type=int, default=256, help="expert count (lower it only to size a profiler capture)")
