@@ -360,6 +360,10 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         raise RuntimeError(f"device status {impl.device_status()}")
     stage_ms = [sum(evs[j].elapsed_time(evs[j + 1]) for evs in stage_ev) / steps for j in range(5)]
     kernel_clocks = capi.read_kernel_clocks(impl._workspace)  # SM clock inside the GEMM kernels of the last step
+    stage_by_rank = None
+    if world > 1:  # barriers sit inside the first and the last stage: show every rank's split
+        stage_by_rank = [None] * world
+        dist.all_gather_object(stage_by_rank, [round(v, 4) for v in stage_ms] + [kernel_clocks["gate_up_gemm"]])
 
     if args.skip_extras:
         if rank == 0:
@@ -467,6 +471,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "clocks": dict(clocks.summary(), in_kernel_sm_mhz=kernel_clocks),
             "roofline": roof,
             "stage_ms": dict(zip(stage_names, stage_ms)),
+            "stage_ms_by_rank": stage_by_rank,
             "layer_roofline_ms": layer_roof_ms, "layer_roofline_frac": layer_roof_ms / ms_step,
             "latency_us": ms_step * 1e3,
             "verify": "ok" if passed else "FAIL", "rel_err": check.rel_err,

@@ -66,7 +66,10 @@ int64_t mb200_dist_workspace_bytes(int precision, int64_t tokens, int hidden, in
   if (check_shape(tokens * world, hidden, intermediate, local_experts, topk)) return -1;
   if (precision == MB200_PRECISION_FP8 && check_shape_fp8(hidden, intermediate)) return -1;
   const Layout l = make_layout(precision, tokens * world, hidden, intermediate, local_experts, topk);
-  return l.total + 2 * up1k(tokens * world * topk * 4);
+  // + ring-ordered routing of all ranks + (tensor parallel) every rank's staged tokens and scales
+  const int64_t eb = precision == MB200_PRECISION_FP8 ? 1 : 2;
+  return l.total + 2 * up1k(tokens * world * topk * 4) + up1k(tokens * world * hidden * eb) +
+         up1k(tokens * world * (hidden / 128) * 4);
 }
 
 int mb200_peer_barrier(void* const* symmetric_ptrs, int rank, int world, uint32_t seq, int32_t* status,
@@ -106,9 +109,10 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
                 (long long)symmetric_bytes, (long long)sl.total);
   const Layout l = make_layout(precision, all_tokens, hidden, intermediate, local_experts, topk);
   const int64_t routing_bytes = up1k(all_tokens * topk * 4);
-  MB200_REQUIRE(workspace_bytes >= l.total + 2 * routing_bytes, kWorkspaceTooSmall,
-                "dist_forward: workspace %lld < %lld bytes", (long long)workspace_bytes,
-                (long long)(l.total + 2 * routing_bytes));
+  const int64_t need_ws = l.total + 2 * routing_bytes + up1k(all_tokens * hidden * (fp8 ? 1 : 2)) +
+                          up1k(all_tokens * (hidden / 128) * 4);
+  MB200_REQUIRE(workspace_bytes >= need_ws, kWorkspaceTooSmall, "dist_forward: workspace %lld < %lld bytes",
+                (long long)workspace_bytes, (long long)need_ws);
   MB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, kInvalidArgument,
                 "dist_forward: workspace must be 1024-byte aligned");
   for (int i = 0; i < world; ++i)
@@ -149,10 +153,31 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   if ((rc = launch_align(ids_all, all_tokens * topk, expert_parallel ? expert_map : nullptr, local_experts, sched,
                          cap, reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
   mark_stage(1, s);
-  if ((rc = launch_gather_rows_peer(fp8 ? 1 : 0, offset_table(symmetric_ptrs, world, sl.payload),
-                                    offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world, int(tokens),
-                                    topk, sched, local_experts, hidden, ws + l.xg,
-                                    fp8 ? reinterpret_cast<float*>(ws + l.xs) : nullptr, cap, s))) return rc;
+  if (expert_parallel) {
+    // a token has about one expert per rank: pull each needed row straight into its sorted slot
+    if ((rc = launch_gather_rows_peer(fp8 ? 1 : 0, offset_table(symmetric_ptrs, world, sl.payload),
+                                      offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world,
+                                      int(tokens), topk, sched, local_experts, hidden, ws + l.xg,
+                                      fp8 ? reinterpret_cast<float*>(ws + l.xs) : nullptr, cap, s))) return rc;
+  } else {
+    // tensor parallel: every rank needs every token for all k assignments, so each peer's
+    // token block crosses NVLink once (into the tail of the workspace) and the k-fold
+    // replication into sorted rows reads local memory
+    const int64_t eb = fp8 ? 1 : 2;
+    char* x_all = ws + l.total + 2 * routing_bytes;
+    char* xs_all = x_all + up1k(all_tokens * hidden * eb);
+    if ((rc = launch_gather_blocks_peer(offset_table(symmetric_ptrs, world, sl.payload), rank, world,
+                                        tokens * hidden * eb, x_all, s))) return rc;
+    if (fp8 && (rc = launch_gather_blocks_peer(offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world,
+                                               tokens * (hidden / 128) * 4, xs_all, s))) return rc;
+    PeerTable local_x{}, local_s{};
+    local_x.ptr[0] = x_all;
+    local_s.ptr[0] = xs_all;
+    // one "rank" holding all W*T tokens in ring order
+    if ((rc = launch_gather_rows_peer(fp8 ? 1 : 0, local_x, local_s, 0, 1, int(all_tokens), topk, sched,
+                                      local_experts, hidden, ws + l.xg,
+                                      fp8 ? reinterpret_cast<float*>(ws + l.xs) : nullptr, cap, s))) return rc;
+  }
   mark_stage(2, s);
   // 4. grouped GEMMs and the local pre-reduction into `partial`
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);

@@ -103,6 +103,8 @@ int launch_peer_barrier(const PeerTable& flags, int rank, int world, uint32_t se
                         cudaStream_t stream);
 int launch_gather_routing(const PeerTable& ids, const PeerTable& weights, int rank, int world,
                           int per_rank, int* ids_all, float* weights_all, cudaStream_t stream);
+int launch_gather_blocks_peer(const PeerTable& src, int rank, int world, int64_t bytes_per_rank, void* dst,
+                              cudaStream_t stream);
 int launch_gather_rows_peer(int fp8, const PeerTable& x, const PeerTable& xs, int rank, int world,
                             int tokens, int topk, const Schedule& sched, int local_experts, int hidden,
                             void* out_rows, float* out_scales_t, int64_t row_capacity,

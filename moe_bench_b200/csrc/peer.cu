@@ -73,6 +73,19 @@ __global__ void gather_routing_kernel(PeerTable ids, PeerTable weights, int rank
   }
 }
 
+// Tensor parallel: every rank's staged block (tokens, or their scales) pulled once
+// into one local array in ring order.  `vec_per_rank` counts 16-byte vectors.
+__global__ void gather_blocks_peer_kernel(PeerTable src, int rank, int world, int64_t vec_per_rank,
+                                          uint4* __restrict__ dst) {
+  const int64_t total = vec_per_rank * world;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int ring = int(i / vec_per_rank);
+    const int64_t off = i - int64_t(ring) * vec_per_rank;
+    dst[i] = reinterpret_cast<const uint4*>(src.ptr[(rank + ring) % world])[off];
+  }
+}
+
 // Sorted rows pulled from the source ranks.  n = (ring*T + t)*k + j.
 __global__ void gather_rows_peer_bf16_kernel(PeerTable x, int rank, int world, int tokens, int topk,
                                              const int* __restrict__ sorted_ids,
@@ -193,6 +206,18 @@ int launch_gather_routing(const PeerTable& ids, const PeerTable& weights, int ra
   const int threads = 256;
   gather_routing_kernel<<<grid_for_rows(int64_t(world) * per_rank, threads, 4), threads, 0, stream>>>(
       ids, weights, rank, world, per_rank, ids_all, weights_all);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_gather_blocks_peer(const PeerTable& src, int rank, int world, int64_t bytes_per_rank, void* dst,
+                              cudaStream_t stream) {
+  MB200_REQUIRE(bytes_per_rank % 16 == 0, kUnsupportedShape, "gather_blocks: %lld bytes per rank is not a multiple of 16",
+                (long long)bytes_per_rank);
+  if (bytes_per_rank == 0) return kOk;
+  const int threads = 256;
+  gather_blocks_peer_kernel<<<grid_for_rows(bytes_per_rank / 16 * world, threads, 16), threads, 0, stream>>>(
+      src, rank, world, bytes_per_rank / 16, reinterpret_cast<uint4*>(dst));
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
