@@ -231,8 +231,27 @@ def _time_vllm_baseline(prob, world, dev, flops_step, barrier, max_over_ranks, o
 
     from moe_bench_b200 import baselines as B
 
+    def agree(flag: float) -> bool:
+        """True only if every rank says so (no collective of the baseline runs otherwise)."""
+        if world == 1:
+            return flag > 0
+        t = torch.tensor([flag], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item() > 0)
+
+    reason, run = "", None
     try:
-        run = B.vllm_compute_only(prob) if world == 1 else B.vllm_serial_scheme(prob, world)
+        local = B.vllm_compute_only(prob)
+        local()  # compiles the Triton kernels; a failure here involves no other rank
+        torch.cuda.synchronize()
+        run = local if world == 1 else B.vllm_serial_scheme(prob, world)
+    except Exception as exc:  # noqa: BLE001
+        reason, run = f"{type(exc).__name__}: {str(exc)[:200]}", None
+    if not agree(1.0 if run is not None else 0.0):
+        return {"unavailable": reason or "vLLM baseline could not be set up on another rank"}
+    ms = diff = 0.0
+    ok = 1.0
+    try:
         for _ in range(3):
             res = run()
         barrier()
@@ -245,14 +264,10 @@ def _time_vllm_baseline(prob, world, dev, flops_step, barrier, max_over_ranks, o
         torch.cuda.synchronize()
         ms = max_over_ranks(s.elapsed_time(e) / n)
         diff = float((res.float() - ours.float()).norm() / ours.float().norm().clamp_min(1e-12))
-        ok = 1.0
     except Exception as exc:  # noqa: BLE001
-        ms, diff, ok, reason = 0.0, 0.0, 0.0, f"{type(exc).__name__}: {str(exc)[:200]}"
-    if world > 1:  # every rank must agree on success before rank 0 reports
-        flag = torch.tensor([ok], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if flag.item() == 0 and ok:
-            ok, reason = 0.0, "failed on another rank"
+        ok, reason = 0.0, f"{type(exc).__name__}: {str(exc)[:200]}"
+        if world > 1:
+            raise  # a rank that fails inside the collectives cannot be recovered from
     if not ok:
         return {"unavailable": reason}
     return {
