@@ -16,6 +16,7 @@ import torch
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libmoe_bench_b200.so")
 
+ABI_VERSION = 2
 PRECISION_BF16 = 0
 PRECISION_FP8 = 1
 PAD_ROWS_BF16 = 16
@@ -89,6 +90,11 @@ def load() -> ctypes.CDLL:
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
+        if lib.mb200_abi_version() != ABI_VERSION:
+            raise MB200Error(
+                f"{LIB_PATH} has ABI version {lib.mb200_abi_version()}, this package needs {ABI_VERSION}: "
+                "rebuild with `python -m moe_bench_b200.build --force`"
+            )
         _lib = lib
     return _lib
 

@@ -106,6 +106,8 @@ Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, 
   l.act = take(cap * intermediate * eb);
   l.y = take((a > 0 ? a : 1) * int64_t(hidden) * 2);
   l.xs = l.acts = 0;
+  l.granule_bytes = precision == MB200_PRECISION_FP8 ? 0 : (cap / kPadBf16 + 1) * 4;
+  l.granules = take(l.granule_bytes);
   if (precision == MB200_PRECISION_FP8) {
     l.xs = take(int64_t(hidden / 128) * cap * 4);
     l.acts = take(int64_t(intermediate / 128) * cap * 4);
@@ -129,7 +131,7 @@ int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts,
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
-                   unsigned long long* clock_probe) {
+                   unsigned long long* clock_probe, const FusedDispatch* dispatch) {
   CUtensorMap map_w;
   TokenMaps maps_t;
   GemmArgs g{};
@@ -160,7 +162,8 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
     g.b_half_offset = 0;
     g.out_cols = hidden;
   }
-  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, device, stream);
+  FusedDispatch none{};
+  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, dispatch ? *dispatch : none, device, stream);
 }
 
 int check_shape_fp8(int hidden, int intermediate) {
@@ -316,12 +319,22 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
   if ((rc = launch_align(topk_ids, tokens * topk, expert_map, local_experts, sched, cap,
                          reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
   mark_stage(1, s);
-  if ((rc = launch_gather_rows_bf16(reinterpret_cast<const __nv_bfloat16*>(hidden_states), sched, local_experts,
-                                    topk, hidden, xg, cap, s))) return rc;
+  // the row gather runs inside the gate/up GEMM kernel (dispatch warps); only its counters are reset here
+  FusedDispatch disp{};
+  disp.src.ptr[0] = const_cast<void*>(hidden_states);
+  disp.rank = 0;
+  disp.world = 1;
+  disp.tokens_per_rank = int(tokens);
+  disp.topk = topk;
+  disp.vec_per_row = hidden / 8;
+  disp.rows_out = reinterpret_cast<uint4*>(xg);
+  disp.granule_done = reinterpret_cast<int*>(ws + l.granules);
+  disp.enabled = 1;
+  MB200_CHECK_CUDA(cudaMemsetAsync(disp.granule_done, 0, size_t(l.granule_bytes), s));
   mark_stage(2, s);
   if ((rc = run_gemm_stage(kGateUpSwiglu, xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, nullptr, act, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8)))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 8), &disp))) return rc;
   mark_stage(3, s);
   if ((rc = run_gemm_stage(kDownWeighted, act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s,

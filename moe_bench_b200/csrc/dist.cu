@@ -9,7 +9,9 @@
 //      quantised to e4m3 + 1x128 scales first, so fp8 travels on the wire);
 //   2. barrier;
 //   3. routing of all ranks -> ring-ordered local copy; sort-and-pad against this
-//      rank's experts; dispatch = pull the needed rows from their owners;
+//      rank's experts; dispatch = pull the needed rows from their owners (bf16: by
+//      the dispatch warps inside the gate/up GEMM kernel, overlapped with its tiles;
+//      fp8: by a gather kernel);
 //   4. the two grouped GEMMs; the contributions of a token that landed on this
 //      rank are pre-reduced into one row of `partial`;
 //   5. barrier; the token's own rank pulls and sums the partial rows; barrier.
@@ -153,12 +155,20 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   if ((rc = launch_align(ids_all, all_tokens * topk, expert_parallel ? expert_map : nullptr, local_experts, sched,
                          cap, reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
   mark_stage(1, s);
+  FusedDispatch disp{};  // bf16: the dispatch pulls run inside the gate/up GEMM kernel
   if (expert_parallel) {
     // a token has about one expert per rank: pull each needed row straight into its sorted slot
-    if ((rc = launch_gather_rows_peer(fp8 ? 1 : 0, offset_table(symmetric_ptrs, world, sl.payload),
-                                      offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world,
-                                      int(tokens), topk, sched, local_experts, hidden, ws + l.xg,
-                                      fp8 ? reinterpret_cast<float*>(ws + l.xs) : nullptr, cap, s))) return rc;
+    if (fp8) {
+      if ((rc = launch_gather_rows_peer_fp8(offset_table(symmetric_ptrs, world, sl.payload),
+                                        offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world,
+                                        int(tokens), topk, sched, local_experts, hidden, ws + l.xg,
+                                        reinterpret_cast<float*>(ws + l.xs), cap, s))) return rc;
+    } else {
+      disp.src = offset_table(symmetric_ptrs, world, sl.payload);
+      disp.rank = rank;
+      disp.world = world;
+      disp.tokens_per_rank = int(tokens);
+    }
   } else {
     // tensor parallel: every rank needs every token for all k assignments, so each peer's
     // token block crosses NVLink once (into the tail of the workspace) and the k-fold
@@ -170,13 +180,27 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
                                         tokens * hidden * eb, x_all, s))) return rc;
     if (fp8 && (rc = launch_gather_blocks_peer(offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world,
                                                tokens * (hidden / 128) * 4, xs_all, s))) return rc;
-    PeerTable local_x{}, local_s{};
-    local_x.ptr[0] = x_all;
-    local_s.ptr[0] = xs_all;
-    // one "rank" holding all W*T tokens in ring order
-    if ((rc = launch_gather_rows_peer(fp8 ? 1 : 0, local_x, local_s, 0, 1, int(all_tokens), topk, sched,
-                                      local_experts, hidden, ws + l.xg,
-                                      fp8 ? reinterpret_cast<float*>(ws + l.xs) : nullptr, cap, s))) return rc;
+    if (fp8) {
+      PeerTable local_x{}, local_s{};
+      local_x.ptr[0] = x_all;
+      local_s.ptr[0] = xs_all;
+      // one "rank" holding all W*T tokens in ring order
+      if ((rc = launch_gather_rows_peer_fp8(local_x, local_s, 0, 1, int(all_tokens), topk, sched, local_experts,
+                                        hidden, ws + l.xg, reinterpret_cast<float*>(ws + l.xs), cap, s))) return rc;
+    } else {
+      disp.src.ptr[0] = x_all;
+      disp.rank = 0;
+      disp.world = 1;
+      disp.tokens_per_rank = int(all_tokens);
+    }
+  }
+  if (!fp8) {
+    disp.topk = topk;
+    disp.vec_per_row = hidden / 8;
+    disp.rows_out = reinterpret_cast<uint4*>(ws + l.xg);
+    disp.granule_done = reinterpret_cast<int*>(ws + l.granules);
+    disp.enabled = 1;
+    MB200_CHECK_CUDA(cudaMemsetAsync(disp.granule_done, 0, size_t(l.granule_bytes), s));
   }
   mark_stage(2, s);
   // 4. grouped GEMMs and the local pre-reduction into `partial`
@@ -195,7 +219,7 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   } else {
     if ((rc = run_gemm_stage(kGateUpSwiglu, ws + l.xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, nullptr, ws + l.act, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8)))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 8), &disp))) return rc;
     mark_stage(3, s);
     if ((rc = run_gemm_stage(kDownWeighted, ws + l.act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, weights_all, y, status, device, s,

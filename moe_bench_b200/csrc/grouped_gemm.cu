@@ -16,9 +16,16 @@
 // baseline.py:62-76 and the ThunderKittens grouped GEMM of
 // kernels/tileoverlap/common/sm120_common.cuh:149-274).
 //
-// One persistent CTA per SM, 320 threads: warp 0 issues TMA loads into a ring of
+// One persistent CTA per SM, 448 threads: warp 0 issues TMA loads into a ring of
 // 128-byte-swizzled stages, warp 1 owns tensor memory and issues tcgen05.mma,
-// warps 2-9 drain the accumulators (tcgen05.ld) and write the output.  The token
+// warps 2-9 drain the accumulators (tcgen05.ld) and write the output, warps
+// 10-13 are the fused dispatch of the gate/up GEMM: they copy token rows (local,
+// or P2P loads from the source ranks over NVLink) into the sorted row buffer one
+// 16-row granule at a time, granules strided over the CTAs in row order, and
+// count each granule's arrival; the TMA warp starts a tile only when all
+// granules of its token block have arrived (acquire on the counters, then a
+// proxy fence).  Dispatch warps never wait, so a cooperative launch (all CTAs
+// resident) makes the scheme deadlock-free.  The token
 // box (16/32/64/128/256 rows), the stage size, the number of stages and whether
 // the accumulators are double-buffered (token box <= 128) are derived on the
 // device from the largest expert segment in the schedule, so one launch suits a
@@ -36,7 +43,10 @@ constexpr int kMaxStages = 8;
 constexpr int kTmemCols = 512;
 constexpr int kEpilogueWarps = 8;
 constexpr int kFirstEpilogueWarp = 2;
-constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
+constexpr int kDispatchWarps = 4;  // warps 10-13: fused dispatch (gate/up GEMM only)
+constexpr int kDispatchLoads = 14;  // 16-byte loads each dispatch lane keeps in flight
+constexpr int kFirstDispatchWarp = kFirstEpilogueWarp + kEpilogueWarps;
+constexpr int kThreads = (kFirstDispatchWarp + kDispatchWarps) * 32;
 constexpr int kMaxTokens = 256;
 
 struct SmemTail {
@@ -131,7 +141,8 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
-                         const __grid_constant__ TokenMaps maps_t, const GemmArgs args) {
+                         const __grid_constant__ TokenMaps maps_t, const GemmArgs args,
+                         const FusedDispatch disp) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -222,6 +233,30 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const TileCoord tc = decode_tile(tile, tail, args.counts, E, args.n_tiles, geo.tb_rows);
       const int w_row = tc.expert * args.b_rows_per_expert;
+      if (kMode == kGateUpSwiglu && disp.enabled) {
+        // all 16-row granules of this token block must have been dispatched
+        const int g0 = tc.row0 / kPad, ng = tc.ntok / kPad;  // ng <= 16
+        uint32_t spins = 0;
+        while (true) {
+          int v = kDispatchWarps;
+          if (lane < ng)
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(disp.granule_done + g0 + lane) : "memory");
+          if (__all_sync(0xffffffffu, v >= kDispatchWarps)) break;
+          if ((++spins & 0x3F) == 0) {
+            if (*ctx.abort_flag) { ok = false; break; }
+            if (global_timer_ns() - ctx.t0 > kWaitLimitNs) {
+              *ctx.abort_flag = 1;
+              if (ctx.status) atomicCAS(ctx.status, 0, kDevWaitTimeout + 6);
+              ok = false;
+              break;
+            }
+            __nanosleep(128);
+          }
+        }
+        if (!ok) break;
+        // rows were written with ordinary stores by other SMs; the TMA engine reads them
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       for (int kb = 0; kb < args.k_iters; ++kb) {
         ok = mbar_wait(smem_u32(&tail->empty[stage]), phase ^ 1, ctx, 1);
         if (!ok) break;
@@ -283,6 +318,41 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       }
       if (ok && lane == 0) tc_commit(smem_u32(&tail->acc_full[buf]));
       __syncwarp();
+    }
+  } else if (warp >= kFirstDispatchWarp) {
+    // ---------------- fused dispatch (gate/up GEMM): fill the sorted row buffer ----------------
+    if (kMode == kGateUpSwiglu && disp.enabled) {
+      const int dw = warp - kFirstDispatchWarp;
+      const int granules = tail->prefix[E];
+      for (int g = blockIdx.x; g < granules; g += gridDim.x) {
+        // each of the 4 dispatch warps takes 4 of the granule's 16 rows
+        for (int i = dw; i < kPad; i += kDispatchWarps) {
+          const int row = g * kPad + i;
+          const int n = __ldg(args.sorted_ids + row);
+          if (n >= 0) {
+            const int tok_global = n / disp.topk;
+            const int ring = tok_global / disp.tokens_per_rank;
+            const int t = tok_global - ring * disp.tokens_per_rank;
+            const uint4* src = reinterpret_cast<const uint4*>(disp.src.ptr[(disp.rank + ring) % disp.world]) +
+                               size_t(t) * disp.vec_per_row;
+            uint4* dst = disp.rows_out + size_t(row) * disp.vec_per_row;
+            // kDispatchLoads 16-byte loads in flight per lane: a load over NVLink takes microseconds and
+            // only 4 warps per SM do this work
+            for (int v0 = lane; v0 < disp.vec_per_row; v0 += 32 * kDispatchLoads) {
+              uint4 buf[kDispatchLoads];
+#pragma unroll
+              for (int u = 0; u < kDispatchLoads; ++u)
+                if (v0 + u * 32 < disp.vec_per_row) buf[u] = src[v0 + u * 32];
+#pragma unroll
+              for (int u = 0; u < kDispatchLoads; ++u)
+                if (v0 + u * 32 < disp.vec_per_row) dst[v0 + u * 32] = buf[u];
+            }
+          }
+        }
+        __threadfence();  // this warp's rows before its arrival count
+        __syncwarp();
+        if (lane == 0) atomicAdd(disp.granule_done + g, 1);
+      }
     }
   } else {
     // ---------------- epilogue: 8 warps, one accumulator row (feature) per thread ----------------
@@ -387,9 +457,12 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
 }  // namespace
 
 int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
-                             const GemmArgs& args, int device, cudaStream_t stream) {
+                             const GemmArgs& args, const FusedDispatch& dispatch, int device,
+                             cudaStream_t stream) {
   MB200_REQUIRE(args.num_experts >= 1 && args.num_experts <= kMaxExperts, kUnsupportedShape,
                 "grouped_gemm: %d local experts, supported 1..%d", args.num_experts, kMaxExperts);
+  MB200_REQUIRE(!dispatch.enabled || mode == kGateUpSwiglu, kInvalidArgument,
+                "grouped_gemm: fused dispatch belongs to the gate/up stage");
   static bool configured[64][2] = {};
   int sms = 0;
   MB200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
@@ -400,8 +473,17 @@ int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const Toke
                                           int(kSmemBytes)));
     configured[device][mode] = true;
   }
-  kernel<<<sms, kThreads, kSmemBytes, stream>>>(map_w, maps_t, args);
-  MB200_CHECK_CUDA(cudaGetLastError());
+  if (dispatch.enabled) {
+    // the tile loader waits for rows that other CTAs' dispatch warps deliver: all
+    // CTAs must be resident, which a cooperative launch guarantees (or refuses)
+    void* params[] = {const_cast<CUtensorMap*>(&map_w), const_cast<TokenMaps*>(&maps_t),
+                      const_cast<GemmArgs*>(&args), const_cast<FusedDispatch*>(&dispatch)};
+    MB200_CHECK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(sms), dim3(kThreads),
+                                                 params, kSmemBytes, stream));
+  } else {
+    kernel<<<sms, kThreads, kSmemBytes, stream>>>(map_w, maps_t, args, dispatch);
+    MB200_CHECK_CUDA(cudaGetLastError());
+  }
   return kOk;
 }
 

@@ -11,6 +11,11 @@ constexpr int kTileM = 128;        // fp8 path: rows per M tile; expert segments
 constexpr int kPadBf16 = 16;       // bf16 path: expert segments are padded to 16 rows
 constexpr int kMaxExperts = 1024;  // local experts per rank supported by the kernels
 
+constexpr int kMaxPeers = 16;
+struct PeerTable {
+  void* ptr[kMaxPeers];  // one pointer per rank, valid in this process
+};
+
 // Output of the sort-and-pad step, all in device memory.
 struct Schedule {
   int* counts;        // [E]    real rows per local expert
@@ -30,9 +35,6 @@ int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map
                  cudaStream_t stream);
 
 // ---- rows.cu ------------------------------------------------------------------------
-int launch_gather_rows_bf16(const __nv_bfloat16* x, const Schedule& sched, int local_experts,
-                            int topk, int hidden, __nv_bfloat16* xg, int64_t row_capacity,
-                            cudaStream_t stream);
 int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, int topk,
                         int hidden, __nv_bfloat16* out, cudaStream_t stream);
 // Per-row, per-128-group e4m3 quantisation.  scales_t is [K/128][scale_ld] (group-major).
@@ -60,6 +62,20 @@ struct GemmArgs {
   unsigned long long* clock_probe;  // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel
 };
 enum GemmMode : int { kGateUpSwiglu = 0, kDownWeighted = 1 };
+// Dispatch fused into the gate/up GEMM: extra warps of every CTA fill the sorted
+// row buffer 16-row granule by granule (from this GPU's tokens, or from the
+// source ranks' staged tokens over NVLink) while the tensor pipeline consumes
+// granules that have already arrived.
+struct FusedDispatch {
+  PeerTable src;          // [rank] -> tokens [tokens_per_rank][hidden] bf16 of that rank
+  int rank, world;        // flat assignment n = ((ring*T + t)*topk + j), ring = (src - rank) mod world
+  int tokens_per_rank;
+  int topk;
+  int vec_per_row;        // hidden / 8 (16-byte vectors per row)
+  uint4* rows_out;        // sorted row buffer the GEMM's token operand is loaded from
+  int* granule_done;      // [row_capacity / 16] arrival counters, zeroed before the launch
+  int enabled;
+};
 // Token-operand tensor maps with boxes of 16, 32, 64, 128 and 256 rows; the
 // kernel picks one from the largest expert segment it finds in the schedule.
 constexpr int kTokenBoxes = 5;
@@ -67,7 +83,8 @@ struct TokenMaps {
   CUtensorMap m[kTokenBoxes];
 };
 int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
-                             const GemmArgs& args, int device, cudaStream_t stream);
+                             const GemmArgs& args, const FusedDispatch& dispatch, int device,
+                             cudaStream_t stream);
 
 // grouped_gemm_fp8.cu: e4m3 operands, fp32 block scales applied in the epilogue
 struct GemmFp8Args {
@@ -95,20 +112,15 @@ int launch_grouped_gemm_fp8(GemmMode mode, const CUtensorMap& map_a, const CUten
                             const GemmFp8Args& args, int device, cudaStream_t stream);
 
 // ---- peer.cu: cross-GPU stages over peer-mapped memory -------------------------------------
-constexpr int kMaxPeers = 16;
-struct PeerTable {
-  void* ptr[kMaxPeers];  // one pointer per rank, valid in this process
-};
 int launch_peer_barrier(const PeerTable& flags, int rank, int world, uint32_t seq, int* status,
                         cudaStream_t stream);
 int launch_gather_routing(const PeerTable& ids, const PeerTable& weights, int rank, int world,
                           int per_rank, int* ids_all, float* weights_all, cudaStream_t stream);
 int launch_gather_blocks_peer(const PeerTable& src, int rank, int world, int64_t bytes_per_rank, void* dst,
                               cudaStream_t stream);
-int launch_gather_rows_peer(int fp8, const PeerTable& x, const PeerTable& xs, int rank, int world,
-                            int tokens, int topk, const Schedule& sched, int local_experts, int hidden,
-                            void* out_rows, float* out_scales_t, int64_t row_capacity,
-                            cudaStream_t stream);
+int launch_gather_rows_peer_fp8(const PeerTable& x, const PeerTable& xs, int rank, int world, int tokens, int topk,
+                                const Schedule& sched, int local_experts, int hidden, void* out_rows,
+                                float* out_scales_t, int64_t row_capacity, cudaStream_t stream);
 int launch_reduce_partials(const PeerTable& partial, int rank, int world, int tokens, int topk,
                            const int* topk_ids, int experts_per_rank, int hidden, __nv_bfloat16* out,
                            cudaStream_t stream);
@@ -117,6 +129,8 @@ int launch_reduce_partials(const PeerTable& partial, int rank, int world, int to
 struct Layout {
   int64_t status, counts, prefix, sorted, inverse, scratch, xg, act, y, total;
   int64_t xs, acts;  // fp8 only: transposed activation scales [K/128][cap], [N/128][cap]
+  int64_t granules;  // bf16 only: arrival counter per 16-row granule of the sorted row buffer
+  int64_t granule_bytes;
 };
 Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk);
 int64_t row_capacity(int64_t tokens, int topk, int local_experts, int pad_rows);
@@ -126,7 +140,7 @@ int check_shape_fp8(int hidden, int intermediate);
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
-                   unsigned long long* clock_probe = nullptr);
+                   unsigned long long* clock_probe = nullptr, const FusedDispatch* dispatch = nullptr);
 int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,

@@ -15,10 +15,12 @@
 //   gather_routing    all ranks' topk ids / weights -> one local array in ring
 //                     order (own rank first), replacing the two small
 //                     all-gathers of schemes.py:122-127 / tk_scheme.py:682-683.
-//   dispatch gathers  EP dispatch (replaces the all-gather of schemes.py:121):
+//   dispatch gather   EP dispatch, fp8 (replaces the all-gather of schemes.py:121):
 //                     the expert rank pulls the token rows routed to its experts
 //                     straight into its sorted, padded row buffer - e4m3 rows plus
-//                     their 1x128 scales (fp8 on the wire) or bf16 rows.
+//                     their 1x128 scales (fp8 on the wire).  The bf16 dispatch runs
+//                     inside the gate/up GEMM kernel (grouped_gemm.cu).
+//   gather_blocks     TP: every rank's staged token block, pulled once.
 //   reduce_partials   EP combine / TP output reduce (replaces the reduce-scatter
 //                     of schemes.py:142): every expert rank has pre-reduced the
 //                     contributions of a token that landed on it into one row;
@@ -87,28 +89,6 @@ __global__ void gather_blocks_peer_kernel(PeerTable src, int rank, int world, in
 }
 
 // Sorted rows pulled from the source ranks.  n = (ring*T + t)*k + j.
-__global__ void gather_rows_peer_bf16_kernel(PeerTable x, int rank, int world, int tokens, int topk,
-                                             const int* __restrict__ sorted_ids,
-                                             const int* __restrict__ mtile_prefix, int local_experts,
-                                             int vec_per_row, uint4* __restrict__ xg, int64_t row_capacity,
-                                             int pad) {
-  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * pad;
-  if (rows > row_capacity) rows = row_capacity;
-  const int warps_per_block = blockDim.x >> 5;
-  const int lane = threadIdx.x & 31;
-  for (int64_t row = int64_t(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
-       row += int64_t(gridDim.x) * warps_per_block) {
-    const int n = __ldg(sorted_ids + row);
-    if (n < 0) continue;
-    const int tok_global = n / topk;
-    const int ring = tok_global / tokens;
-    const int t = tok_global - ring * tokens;
-    const uint4* src = reinterpret_cast<const uint4*>(x.ptr[(rank + ring) % world]) + int64_t(t) * vec_per_row;
-    uint4* dst = xg + row * vec_per_row;
-    for (int v = lane; v < vec_per_row; v += 32) dst[v] = src[v];
-  }
-}
-
 // e4m3 rows + their scales ([T][K/128] at the source) -> sorted rows + group-major scales.
 __global__ void gather_rows_peer_fp8_kernel(PeerTable xq, PeerTable xs, int rank, int world, int tokens,
                                             int topk, const int* __restrict__ sorted_ids,
@@ -222,22 +202,15 @@ int launch_gather_blocks_peer(const PeerTable& src, int rank, int world, int64_t
   return kOk;
 }
 
-int launch_gather_rows_peer(int fp8, const PeerTable& x, const PeerTable& xs, int rank, int world, int tokens,
-                            int topk, const Schedule& sched, int local_experts, int hidden, void* out_rows,
-                            float* out_scales_t, int64_t row_capacity, cudaStream_t stream) {
+int launch_gather_rows_peer_fp8(const PeerTable& x, const PeerTable& xs, int rank, int world, int tokens, int topk,
+                                const Schedule& sched, int local_experts, int hidden, void* out_rows,
+                                float* out_scales_t, int64_t row_capacity, cudaStream_t stream) {
   const int threads = 256;
   const int blocks = grid_for_rows(row_capacity * 32, threads, 16);
-  if (fp8) {
-    MB200_REQUIRE(hidden % 128 == 0, kUnsupportedShape, "dispatch: hidden=%d must be a multiple of 128", hidden);
-    gather_rows_peer_fp8_kernel<<<blocks, threads, 0, stream>>>(
-        x, xs, rank, world, tokens, topk, sched.sorted_ids, sched.mtile_prefix, local_experts, hidden / 128,
-        reinterpret_cast<uint4*>(out_rows), out_scales_t, row_capacity, sched.pad_rows);
-  } else {
-    MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "dispatch: hidden=%d must be a multiple of 8", hidden);
-    gather_rows_peer_bf16_kernel<<<blocks, threads, 0, stream>>>(
-        x, rank, world, tokens, topk, sched.sorted_ids, sched.mtile_prefix, local_experts, hidden / 8,
-        reinterpret_cast<uint4*>(out_rows), row_capacity, sched.pad_rows);
-  }
+  MB200_REQUIRE(hidden % 128 == 0, kUnsupportedShape, "dispatch: hidden=%d must be a multiple of 128", hidden);
+  gather_rows_peer_fp8_kernel<<<blocks, threads, 0, stream>>>(
+      x, xs, rank, world, tokens, topk, sched.sorted_ids, sched.mtile_prefix, local_experts, hidden / 128,
+      reinterpret_cast<uint4*>(out_rows), out_scales_t, row_capacity, sched.pad_rows);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -1,13 +1,14 @@
 // Row-wise, bandwidth-bound stages around the grouped GEMMs:
-//   gather_rows:   xg[row, :] = x[token(row), :] for the sorted assignment rows
-//                  (the reference replicates every token k times instead,
-//                  reference.py:103).
+//   gather_quant:  fp8 path: xq[row, :] = e4m3(x[token(row), :]) for the sorted
+//                  assignment rows (the reference replicates every token k times
+//                  instead, reference.py:130-145).  The bf16 path gathers inside
+//                  the gate/up GEMM kernel.
 //   combine:       out[t, :] = sum over the k local assignments of token t of
 //                  the already weighted rows y[t*k + j, :], fp32 sum, bf16 store
 //                  (reference.py:180-182).
 //   group_quant:   per row, per 128-wide group dynamic e4m3 quantisation of
 //                  activations (reference.py:143-145,157-163).
-// All three move 16 bytes per thread per access and size their grids as a
+// All of them move 16 bytes per thread per access and size their grids as a
 // multiple of the SM count.
 
 #include "layer.cuh"
@@ -15,25 +16,6 @@
 namespace mb200 {
 
 namespace {
-
-__global__ void gather_rows_bf16_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted_ids,
-                                        const int* __restrict__ mtile_prefix, int local_experts,
-                                        int topk, int vec_per_row, uint4* __restrict__ xg,
-                                        int64_t row_capacity, int pad) {
-  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * pad;
-  if (rows > row_capacity) rows = row_capacity;
-  // one warp per row, rows strided over all warps of the grid
-  const int warps_per_block = blockDim.x >> 5;
-  const int lane = threadIdx.x & 31;
-  for (int64_t row = int64_t(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
-       row += int64_t(gridDim.x) * warps_per_block) {
-    const int n = __ldg(sorted_ids + row);
-    if (n < 0) continue;  // padding rows are never read back
-    const uint4* src = x + int64_t(n / topk) * vec_per_row;
-    uint4* dst = xg + row * vec_per_row;
-    for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
-  }
-}
 
 __device__ __forceinline__ void accumulate_bf16x8(const uint4& v, float (&acc)[8]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -173,20 +155,6 @@ int sm_count() {
 }
 
 }  // namespace
-
-int launch_gather_rows_bf16(const __nv_bfloat16* x, const Schedule& sched, int local_experts,
-                            int topk, int hidden, __nv_bfloat16* xg, int64_t row_capacity,
-                            cudaStream_t stream) {
-  MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "gather_rows: hidden=%d must be a multiple of 8", hidden);
-  const int threads = 256;
-  // the row count lives on the device: size the grid for the capacity
-  const int blocks = grid_for(row_capacity * 32, threads, sm_count(), 16);
-  gather_rows_bf16_kernel<<<blocks, threads, 0, stream>>>(
-      reinterpret_cast<const uint4*>(x), sched.sorted_ids, sched.mtile_prefix, local_experts, topk,
-      hidden / 8, reinterpret_cast<uint4*>(xg), row_capacity, sched.pad_rows);
-  MB200_CHECK_CUDA(cudaGetLastError());
-  return kOk;
-}
 
 int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, int topk, int hidden,
                         __nv_bfloat16* out, cudaStream_t stream) {
