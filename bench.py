@@ -471,10 +471,15 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         })
         layer_bytes = touched * 3 * n_local * HIDDEN * wb + 2 * tokens * HIDDEN * 2 + assignments * 8
         layer_roof_ms = max(layer_bytes / (peaks["hbm_gbs"] * 1e9), flops_step / (tc_peak * 1e12)) * 1e3
-        if world == 1:
-            kernels_per_step = 7 if assignments > 16384 else 5
-        else:  # 3 barriers, routing gather, align, dispatch, 2 GEMMs, partial combine, reduce (+ quantise)
-            kernels_per_step = 9 + (3 if assignments * world > 16384 else 1) + (1 if fp8 else 0)
+        # kernels of this library launched per step (memsets and copies are not kernels)
+        total_assignments = assignments * world
+        n_align = 3 if total_assignments > 16384 else 1
+        if world == 1:      # align, [fp8: gather+quantise], gate/up GEMM (bf16: with the gather fused), down GEMM, combine
+            kernels_per_step = n_align + 3 + (1 if fp8 else 0)
+        else:               # + 3 barriers, routing gather, partial reduce; fp8: quantise + dispatch gather; TP: block gather(s)
+            kernels_per_step = n_align + 3 + 5 + (2 if fp8 else 0)
+            if args.mode == "tp":
+                kernels_per_step += 2 if fp8 else 1
         line = {
             "metric": METRIC, "value": flops_step * world / (ms_step * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
