@@ -171,7 +171,7 @@ def run_reference(args, rank: int, world: int) -> None:
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    _emit(line)
 
 
 class _LazyExperts:
@@ -382,9 +382,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     if args.skip_extras:
         if rank == 0:
-            print(json.dumps({"ms_per_step": ms_step, "stage_ms": dict(zip(stage_names, stage_ms)),
-                              "config": _config_dict(tokens, world, args.precision, args.mode, args.distribution),
-                              "note": "profiling run, extras skipped"}))
+            _emit({"ms_per_step": ms_step, "stage_ms": dict(zip(stage_names, stage_ms)),
+                   "config": _config_dict(tokens, world, args.precision, args.mode, args.distribution),
+                   "note": "profiling run, extras skipped"})
         if world > 1:
             impl.close()
             dist.destroy_process_group()
@@ -500,14 +500,35 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         if world == 1 and not args.no_cpu_baseline and not fp8:  # the CPU leg times the bf16 oracle
             res = _time_cpu_oracle(tokens, 20, 2)
             line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line))
+        _emit(line)
     if world > 1:
         impl.close()
         dist.barrier()
         dist.destroy_process_group()
 
 
+_RESULT_STREAM = None
+
+
+def _claim_stdout() -> None:
+    """Keep the real stdout for the one JSON line and send everything else that
+    writes to file descriptor 1 (vLLM and Triton log there) to stderr."""
+    global _RESULT_STREAM
+    if _RESULT_STREAM is None:
+        sys.stdout.flush()
+        _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+        sys.stdout = sys.stderr
+
+
+def _emit(line: dict) -> None:
+    stream = _RESULT_STREAM or sys.stdout
+    stream.write(json.dumps(line) + "\n")
+    stream.flush()
+
+
 def main() -> None:
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
