@@ -152,6 +152,16 @@ int mb200_grouped_gemm_fp8(int mode, const void* a, const float* a_scale_t, int6
                            const int32_t* sorted_ids, const float* row_scale, void* out,
                            float* out_scale_t, int32_t* status, int device, void* stream);
 
+/* The same two stages on a schedule padded to MB200_PAD_ROWS_BF16 (16 rows), with
+ * the tokens on the MMA N dimension: what the fp8 forward uses when experts get
+ * few rows each (at most 24 on average), where 128-row token tiles would be
+ * mostly padding.  Arguments as mb200_grouped_gemm_fp8. */
+int mb200_grouped_gemm_fp8_cols(int mode, const void* a, const float* a_scale_t, int64_t row_capacity,
+                                const void* w, const float* w_scale, int local_experts, int hidden,
+                                int intermediate, const int32_t* counts, const int32_t* mtile_prefix,
+                                const int32_t* sorted_ids, const float* row_scale, void* out,
+                                float* out_scale_t, int32_t* status, int device, void* stream);
+
 /* The layer forward with fp8 block-quantised weights (reference.py:119-167 +
  * 170-182; baseline.py:62-76 with quant_config).  w1/w2 are e4m3 with fp32
  * scales w1_scale [E_local, 2*intermediate/128, hidden/128] and w2_scale

@@ -20,7 +20,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 OBJ_DIR = os.path.join(PKG, "build")
 LIB_PATH = os.path.join(PKG, "libmoe_bench_b200.so")
-SOURCES = ["api.cu", "route_align.cu", "rows.cu", "grouped_gemm.cu", "grouped_gemm_fp8.cu", "peer.cu", "dist.cu"]
+SOURCES = ["api.cu", "route_align.cu", "rows.cu", "grouped_gemm.cu", "grouped_gemm_fp8.cu", "grouped_gemm_fp8_cols.cu", "peer.cu", "dist.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "--extended-lambda",

@@ -48,6 +48,11 @@ SIGNATURES = {
         [c_i32, c_vp, c_vp, c_i64, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
          c_i32, c_vp],
     ),
+    "mb200_grouped_gemm_fp8_cols": (
+        c_i32,
+        [c_i32, c_vp, c_vp, c_i64, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+         c_i32, c_vp],
+    ),
     "mb200_moe_forward_fp8": (
         c_i32,
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64,
@@ -236,11 +241,13 @@ def moe_forward_bf16(x, w1, w2, topk_ids, topk_weights, expert_map, out, workspa
 
 
 def grouped_gemm_fp8(mode, a, a_scale_t, w, w_scale, hidden, intermediate, counts, prefix, sorted_ids,
-                     row_scale, out, out_scale_t, status):
-    """One fp8 grouped GEMM stage (mode 0 gate/up + SiLU-mul + re-quantise, mode 1 down + weight)."""
+                     row_scale, out, out_scale_t, status, cols: bool = False):
+    """One fp8 grouped GEMM stage (mode 0 gate/up + SiLU-mul + re-quantise, mode 1 down + weight).
+    ``cols``: schedule padded to 16 rows, tokens-on-columns kernel; else 128-row token tiles."""
     dev = a.device
+    fn = load().mb200_grouped_gemm_fp8_cols if cols else load().mb200_grouped_gemm_fp8
     _check(
-        load().mb200_grouped_gemm_fp8(
+        fn(
             mode, _ptr(a), _ptr(a_scale_t), a.shape[0], _ptr(w), _ptr(w_scale), w.shape[0], hidden, intermediate,
             _ptr(counts), _ptr(prefix), _ptr(sorted_ids), _ptr(row_scale), _ptr(out), _ptr(out_scale_t),
             _ptr(status), dev.index or 0, _stream(dev),

@@ -89,10 +89,11 @@ int64_t align_up(int64_t v) { return (v + 1023) / 1024 * 1024; }
 cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 }  // namespace
 
-Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk) {
+Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk,
+                   int pad_rows) {
   const int64_t eb = precision == MB200_PRECISION_FP8 ? 1 : 2;  // bytes per activation element
   const int64_t a = tokens * topk;
-  const int64_t cap = row_capacity(tokens, topk, local_experts, pad_rows_of(precision));
+  const int64_t cap = row_capacity(tokens, topk, local_experts, pad_rows);
   Layout l;
   int64_t off = 0;
   auto take = [&](int64_t bytes) { int64_t o = off; off = align_up(off + bytes); return o; };
@@ -177,10 +178,19 @@ int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t 
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,
                        void* out, float* out_scale_t, int* status, int device, cudaStream_t stream,
-                       unsigned long long* clock_probe) {
+                       unsigned long long* clock_probe, int pad_rows) {
   CUtensorMap map_a, map_b;
   GemmFp8Args g{};
   g.clock_probe = clock_probe;
+  const bool cols = pad_rows == kPadBf16;  // schedule padded to 16 rows: tokens-on-columns kernel
+  TokenMaps maps_t;
+  if (cols) {
+    const int token_cols = mode == kGateUpSwiglu ? hidden : intermediate;
+    for (int i = 0; i < kTokenBoxes; ++i) {
+      int rc0 = make_tensor_map_2d(&maps_t.m[i], a, 1, uint64_t(cap), uint64_t(token_cols), 16u << i);
+      if (rc0) return rc0;
+    }
+  }
   g.counts = counts;
   g.mtile_prefix = prefix;
   g.sorted_ids = sorted;
@@ -214,6 +224,7 @@ int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t 
     g.scale_rows_per_expert = hidden / 128;
     g.scale_half_offset = 0;
   }
+  if (cols) return launch_grouped_gemm_fp8_cols(GemmMode(mode), map_b, maps_t, g, device, stream);
   return launch_grouped_gemm_fp8(GemmMode(mode), map_a, map_b, g, device, stream);
 }
 
@@ -287,7 +298,8 @@ int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int int
     return -1;
   }
   if (precision == MB200_PRECISION_FP8 && check_shape_fp8(hidden, intermediate)) return -1;
-  return make_layout(precision, tokens, hidden, intermediate, local_experts, topk).total;
+  // fp8: the 128-row padding needs the larger buffers; the forward may use the 16-row one
+  return make_layout(precision, tokens, hidden, intermediate, local_experts, topk, pad_rows_of(precision)).total;
 }
 
 int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void* w2,
@@ -300,7 +312,7 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
   if (tokens == 0) return kOk;
   MB200_REQUIRE(hidden_states && w1 && w2 && topk_ids && topk_weights && out && workspace, kInvalidArgument,
                 "moe_forward_bf16: null pointer");
-  const Layout l = make_layout(MB200_PRECISION_BF16, tokens, hidden, intermediate, local_experts, topk);
+  const Layout l = make_layout(MB200_PRECISION_BF16, tokens, hidden, intermediate, local_experts, topk, kPadBf16);
   MB200_REQUIRE(workspace_bytes >= l.total, kWorkspaceTooSmall, "moe_forward_bf16: workspace %lld < %lld bytes",
                 (long long)workspace_bytes, (long long)l.total);
   MB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, kInvalidArgument,
@@ -364,6 +376,26 @@ int mb200_grouped_gemm_fp8(int mode, const void* a, const float* a_scale_t, int6
                             as_stream(stream));
 }
 
+int mb200_grouped_gemm_fp8_cols(int mode, const void* a, const float* a_scale_t, int64_t row_cap, const void* w,
+                                const float* w_scale, int local_experts, int hidden, int intermediate,
+                                const int32_t* counts, const int32_t* mtile_prefix, const int32_t* sorted_ids,
+                                const float* row_scale, void* out, float* out_scale_t, int32_t* status,
+                                int device, void* stream) {
+  MB200_REQUIRE(mode == 0 || mode == 1, kInvalidArgument, "grouped_gemm_fp8_cols: mode=%d", mode);
+  MB200_REQUIRE(a && a_scale_t && w && w_scale && counts && mtile_prefix && sorted_ids && out &&
+                    (mode == 0 ? out_scale_t != nullptr : row_scale != nullptr),
+                kInvalidArgument, "grouped_gemm_fp8_cols: null pointer");
+  MB200_REQUIRE(row_cap > 0 && row_cap % kPadBf16 == 0, kInvalidArgument,
+                "grouped_gemm_fp8_cols: row capacity %lld must be a positive multiple of %d", (long long)row_cap,
+                kPadBf16);
+  int rc = check_shape(0, hidden, intermediate, local_experts, 1);
+  if (rc) return rc;
+  if ((rc = check_shape_fp8(hidden, intermediate))) return rc;
+  return run_gemm_stage_fp8(mode, a, a_scale_t, row_cap, w, w_scale, local_experts, hidden, intermediate, counts,
+                            mtile_prefix, sorted_ids, row_scale, out, out_scale_t, status, device,
+                            as_stream(stream), nullptr, kPadBf16);
+}
+
 int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void* w2, const float* w1_scale,
                           const float* w2_scale, const int32_t* topk_ids, const float* topk_weights,
                           const int32_t* expert_map, void* out, int64_t tokens, int hidden, int intermediate,
@@ -375,17 +407,20 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
   if (tokens == 0) return kOk;
   MB200_REQUIRE(hidden_states && w1 && w2 && w1_scale && w2_scale && topk_ids && topk_weights && out && workspace,
                 kInvalidArgument, "moe_forward_fp8: null pointer");
-  const Layout l = make_layout(MB200_PRECISION_FP8, tokens, hidden, intermediate, local_experts, topk);
-  MB200_REQUIRE(workspace_bytes >= l.total, kWorkspaceTooSmall, "moe_forward_fp8: workspace %lld < %lld bytes",
-                (long long)workspace_bytes, (long long)l.total);
+  // few rows per expert: 16-row padding and the tokens-on-columns kernels; else 128-row tiles
+  const int pad = fp8_pad_rows(tokens * topk, local_experts);
+  const Layout l = make_layout(MB200_PRECISION_FP8, tokens, hidden, intermediate, local_experts, topk, pad);
+  const int64_t need = make_layout(MB200_PRECISION_FP8, tokens, hidden, intermediate, local_experts, topk, kTileM).total;
+  MB200_REQUIRE(workspace_bytes >= need, kWorkspaceTooSmall, "moe_forward_fp8: workspace %lld < %lld bytes",
+                (long long)workspace_bytes, (long long)need);
   MB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, kInvalidArgument,
                 "moe_forward_fp8: workspace must be 1024-byte aligned");
   cudaStream_t s = as_stream(stream);
   char* ws = reinterpret_cast<char*>(workspace);
   int* status = reinterpret_cast<int*>(ws + l.status);
   Schedule sched{reinterpret_cast<int*>(ws + l.counts), reinterpret_cast<int*>(ws + l.prefix),
-                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse), kTileM};
-  const int64_t cap = row_capacity(tokens, topk, local_experts, kTileM);
+                 reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse), pad};
+  const int64_t cap = row_capacity(tokens, topk, local_experts, pad);
   uint8_t* xq = reinterpret_cast<uint8_t*>(ws + l.xg);
   float* xs_t = reinterpret_cast<float*>(ws + l.xs);
   uint8_t* actq = reinterpret_cast<uint8_t*>(ws + l.act);
@@ -401,13 +436,11 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
   mark_stage(2, s);
   if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, xq, xs_t, cap, w1, w1_scale, local_experts, hidden, intermediate,
                                sched.counts, sched.mtile_prefix, sched.sorted_ids, nullptr, actq, acts_t, status,
-                               device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8)))) return rc;
+                               device, s, reinterpret_cast<unsigned long long*>(status + 8), pad))) return rc;
   mark_stage(3, s);
   if ((rc = run_gemm_stage_fp8(kDownWeighted, actq, acts_t, cap, w2, w2_scale, local_experts, hidden, intermediate,
                                sched.counts, sched.mtile_prefix, sched.sorted_ids, topk_weights, y, nullptr, status,
-                               device, s,
-                             reinterpret_cast<unsigned long long*>(status + 12)))) return rc;
+                               device, s, reinterpret_cast<unsigned long long*>(status + 12), pad))) return rc;
   mark_stage(4, s);
   rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
   mark_stage(5, s);

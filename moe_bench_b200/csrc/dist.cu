@@ -67,7 +67,8 @@ int64_t mb200_dist_workspace_bytes(int precision, int64_t tokens, int hidden, in
   if (world < 1 || world > kMaxPeers) return -1;
   if (check_shape(tokens * world, hidden, intermediate, local_experts, topk)) return -1;
   if (precision == MB200_PRECISION_FP8 && check_shape_fp8(hidden, intermediate)) return -1;
-  const Layout l = make_layout(precision, tokens * world, hidden, intermediate, local_experts, topk);
+  const Layout l = make_layout(precision, tokens * world, hidden, intermediate, local_experts, topk,
+                               pad_rows_of(precision));
   // + ring-ordered routing of all ranks + (tensor parallel) every rank's staged tokens and scales
   const int64_t eb = precision == MB200_PRECISION_FP8 ? 1 : 2;
   return l.total + 2 * up1k(tokens * world * topk * 4) + up1k(tokens * world * hidden * eb) +
@@ -109,9 +110,14 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   const SymLayout sl = make_sym_layout(precision, tokens, hidden, topk, world);
   MB200_REQUIRE(symmetric_bytes >= sl.total, kWorkspaceTooSmall, "dist_forward: symmetric buffer %lld < %lld bytes",
                 (long long)symmetric_bytes, (long long)sl.total);
-  const Layout l = make_layout(precision, all_tokens, hidden, intermediate, local_experts, topk);
+  // fp8 with few rows per expert: 16-row padding and the tokens-on-columns kernels
+  const int64_t expected_local = expert_parallel ? all_tokens * topk / world : all_tokens * topk;
+  const int pad = fp8 ? fp8_pad_rows(expected_local, local_experts) : kPadBf16;
+  const Layout l = make_layout(precision, all_tokens, hidden, intermediate, local_experts, topk, pad);
+  const int64_t l_max_total =
+      make_layout(precision, all_tokens, hidden, intermediate, local_experts, topk, pad_rows_of(precision)).total;
   const int64_t routing_bytes = up1k(all_tokens * topk * 4);
-  const int64_t need_ws = l.total + 2 * routing_bytes + up1k(all_tokens * hidden * (fp8 ? 1 : 2)) +
+  const int64_t need_ws = l_max_total + 2 * routing_bytes + up1k(all_tokens * hidden * (fp8 ? 1 : 2)) +
                           up1k(all_tokens * (hidden / 128) * 4);
   MB200_REQUIRE(workspace_bytes >= need_ws, kWorkspaceTooSmall, "dist_forward: workspace %lld < %lld bytes",
                 (long long)workspace_bytes, (long long)need_ws);
@@ -127,10 +133,10 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   int* status = reinterpret_cast<int*>(ws + l.status);
   Schedule sched{reinterpret_cast<int*>(ws + l.counts), reinterpret_cast<int*>(ws + l.prefix),
                  reinterpret_cast<int*>(ws + l.sorted), reinterpret_cast<int*>(ws + l.inverse),
-                 pad_rows_of(precision)};
+                 pad};
   int* ids_all = reinterpret_cast<int*>(ws + l.total);
   float* weights_all = reinterpret_cast<float*>(ws + l.total + routing_bytes);
-  const int64_t cap = row_capacity(all_tokens, topk, local_experts, pad_rows_of(precision));
+  const int64_t cap = row_capacity(all_tokens, topk, local_experts, pad);
   const PeerTable flags = offset_table(symmetric_ptrs, world, sl.flags);
 
   // 1. stage own routing and tokens
@@ -209,13 +215,12 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
     if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, ws + l.xg, reinterpret_cast<float*>(ws + l.xs), cap, w1, w1_scale,
                                  local_experts, hidden, intermediate, sched.counts, sched.mtile_prefix,
                                  sched.sorted_ids, nullptr, ws + l.act, reinterpret_cast<float*>(ws + l.acts), status,
-                                 device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8)))) return rc;
+                                 device, s, reinterpret_cast<unsigned long long*>(status + 8), pad))) return rc;
     mark_stage(3, s);
     if ((rc = run_gemm_stage_fp8(kDownWeighted, ws + l.act, reinterpret_cast<float*>(ws + l.acts), cap, w2, w2_scale,
                                  local_experts, hidden, intermediate, sched.counts, sched.mtile_prefix,
                                  sched.sorted_ids, weights_all, y, nullptr, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 12)))) return rc;
+                                 reinterpret_cast<unsigned long long*>(status + 12), pad))) return rc;
   } else {
     if ((rc = run_gemm_stage(kGateUpSwiglu, ws + l.xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, nullptr, ws + l.act, status, device, s,

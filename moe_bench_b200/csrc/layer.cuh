@@ -110,6 +110,14 @@ struct GemmFp8Args {
 };
 int launch_grouped_gemm_fp8(GemmMode mode, const CUtensorMap& map_a, const CUtensorMap& map_b,
                             const GemmFp8Args& args, int device, cudaStream_t stream);
+// grouped_gemm_fp8_cols.cu: same arithmetic, tokens on the accumulator columns (schedule padded to 16)
+int launch_grouped_gemm_fp8_cols(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
+                                 const GemmFp8Args& args, int device, cudaStream_t stream);
+// Rows per expert up to which the fp8 forward uses the tokens-on-columns kernel.
+constexpr int kFp8ColsMaxAvgRows = 24;  // measured: at 64 rows per expert the 128-row-tile kernel is faster
+inline int fp8_pad_rows(int64_t assignments, int experts) {
+  return assignments <= int64_t(kFp8ColsMaxAvgRows) * experts ? kPadBf16 : kTileM;
+}
 
 // ---- peer.cu: cross-GPU stages over peer-mapped memory -------------------------------------
 int launch_peer_barrier(const PeerTable& flags, int rank, int world, uint32_t seq, int* status,
@@ -132,7 +140,8 @@ struct Layout {
   int64_t granules;  // bf16 only: arrival counter per 16-row granule of the sorted row buffer
   int64_t granule_bytes;
 };
-Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk);
+Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk,
+                   int pad_rows);
 int64_t row_capacity(int64_t tokens, int topk, int local_experts, int pad_rows);
 inline int pad_rows_of(int precision) { return precision == 1 /* fp8 */ ? kTileM : kPadBf16; }
 int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts, int topk);
@@ -145,7 +154,7 @@ int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t 
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,
                        void* out, float* out_scale_t, int* status, int device, cudaStream_t stream,
-                       unsigned long long* clock_probe = nullptr);
+                       unsigned long long* clock_probe = nullptr, int pad_rows = kTileM);
 void mark_stage(int i, cudaStream_t s);
 
 // ---- tensormap.cu ----------------------------------------------------------------------

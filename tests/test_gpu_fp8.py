@@ -38,15 +38,20 @@ def _fp8_problem(tokens, hidden, inter, experts, topk, dist="uniform", seed=0, m
     return P.make_problem(cfg, tokens, rank)
 
 
+@pytest.mark.parametrize("cols", [False, True])
 @pytest.mark.parametrize(
     "tokens,hidden,inter,experts,topk,dist",
     [(64, 256, 128, 8, 2, "uniform"), (300, 512, 256, 4, 2, "uniform"), (40, 1024, 384, 16, 4, "single")],
 )
-def test_fp8_gemm_stages(tokens, hidden, inter, experts, topk, dist):
+def test_fp8_gemm_stages(tokens, hidden, inter, experts, topk, dist, cols):
+    """Both fp8 kernel families: 128-row token tiles, and tokens on the MMA N dimension
+    (schedule padded to 16 rows; 150 rows per expert here means two token blocks)."""
     prob = _fp8_problem(tokens, hidden, inter, experts, topk, dist)
     qc = prob.quant_config
     ids = prob.topk_ids
-    counts, prefix, sorted_ids, inverse = capi.align(ids.to(DEV), None, experts, capi.PAD_ROWS_FP8)
+    counts, prefix, sorted_ids, inverse = capi.align(
+        ids.to(DEV), None, experts, capi.PAD_ROWS_BF16 if cols else capi.PAD_ROWS_FP8
+    )
     cap = sorted_ids.shape[0]
     s_cpu = sorted_ids.cpu()
     rows = (s_cpu >= 0).nonzero().flatten()
@@ -63,7 +68,7 @@ def test_fp8_gemm_stages(tokens, hidden, inter, experts, topk, dist):
     acts_t = torch.zeros(inter // 128, cap, dtype=torch.float32, device=DEV)
     capi.grouped_gemm_fp8(
         0, a.to(DEV), a_s_t.contiguous().to(DEV), prob.w1.to(DEV), qc.w1_scale.contiguous().to(DEV), hidden, inter,
-        counts, prefix, sorted_ids, None, actq, acts_t, status,
+        counts, prefix, sorted_ids, None, actq, acts_t, status, cols=cols,
     )
     torch.cuda.synchronize()
     assert int(status.item()) == 0
@@ -89,7 +94,7 @@ def test_fp8_gemm_stages(tokens, hidden, inter, experts, topk, dist):
     y = torch.full((tokens * topk, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
     capi.grouped_gemm_fp8(
         1, actq, acts_t, prob.w2.to(DEV), qc.w2_scale.contiguous().to(DEV), hidden, inter, counts, prefix,
-        sorted_ids, w.to(DEV), y, None, status,
+        sorted_ids, w.to(DEV), y, None, status, cols=cols,
     )
     torch.cuda.synchronize()
     assert int(status.item()) == 0
