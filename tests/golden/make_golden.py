@@ -38,7 +38,7 @@ def sha(t: torch.Tensor) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-parent", default="/root")
+    ap.add_argument("--ref-parent", required=True, help="directory that contains the reference/ package")
     args = ap.parse_args()
     sys.path.insert(0, args.ref_parent)
     sys.path.insert(0, ROOT)

@@ -79,7 +79,7 @@ def test_noalloc_align_matches_align_on_consecutive_calls():
         assert torch.cuda.mem_get_info()[0] >= free_before
         _same(got, want)
         _same(got_again, want)
-        # drop this round's tensors now, so the next round's measurement sees no frees
+        # drop this iteration's tensors now, so the next iteration's measurement sees no frees
         del got, got_again, want, outs, outs2
 
 
