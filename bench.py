@@ -279,7 +279,7 @@ def _time_vllm_baseline(prob, world, dev, flops_step, barrier, max_over_ranks, o
 
 
 def _config_dict(tokens: int, world: int, precision: str = "bf16", mode: str = "ep", distribution: str = "uniform"):
-    wgb = 22.5 if precision == "bf16" else 11.3
+    wgb = 11.3 if precision == "fp8" else 22.5
     return {
         "workload": f"dsv32_{precision}_compute_only_T{tokens}" + ("" if EXPERTS == 256 else f"_E{EXPERTS}"),
         "tokens_per_gpu": tokens, "hidden": HIDDEN,
@@ -311,7 +311,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     tokens, steps, warmup = args.tokens, args.steps, args.warmup
     fp8 = args.precision == "fp8"
-    prec = P.Precision.FP8 if fp8 else P.Precision.BF16
+    prec = P.Precision(args.precision)
     if world == 1:
         cfg = P.deepseek_v32_config(device=str(dev), num_tokens=[tokens], num_experts=EXPERTS, precision=prec,
                                     routing=P.RoutingConfig(distribution=P.Distribution(args.distribution)))
@@ -465,7 +465,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                     "peak": tc_peak, "unit": "TFLOP/s"}
         roof["frac"] = roof["achieved"] / roof["peak"]
         roof.update({
-            "traffic": None, "kernel": f"grouped_gemm_{args.precision}_kernel<gate_up_swiglu>", "kernel_ms": gemm_ms,
+            "traffic": None, "kernel": f"grouped_gemm_{'fp8' if fp8 else 'bf16'}_kernel<gate_up_swiglu>", "kernel_ms": gemm_ms,
             "peak_source": peaks["source"] + " (burst)", "algorithmic_bytes": gemm_bytes,
             "algorithmic_flops": gemm_flops, "t_hbm_ms": t_hbm * 1e3, "t_tensor_ms": t_tc * 1e3,
         })
@@ -535,8 +535,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=8192, help="tokens per GPU")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8"],
-                    help="bf16 = the headline workload; fp8 = the block-quantised config of the same shape")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8", "fp16"],
+                    help="bf16 = the headline workload; fp8 = the block-quantised config of the same shape; "
+                         "fp16 = the bf16 kernels with IEEE-half tensors")
     ap.add_argument("--mode", default="ep", choices=["ep", "tp"], help="parallel mode when --gpus > 1")
     ap.add_argument("--distribution", default="uniform", choices=["uniform", "single", "skewed", "balanced"])
     ap.add_argument("--no-cpu-baseline", action="store_true")

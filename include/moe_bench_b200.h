@@ -32,9 +32,10 @@
 extern "C" {
 #endif
 
-#define MB200_ABI_VERSION 2
+#define MB200_ABI_VERSION 3
 #define MB200_PRECISION_BF16 0
 #define MB200_PRECISION_FP8 1
+#define MB200_PRECISION_FP16 2 /* the bf16 data flow with IEEE half operands and outputs */
 #define MB200_PAD_ROWS_BF16 16 /* bf16 forward: expert segments are padded to 16 rows */
 #define MB200_PAD_ROWS_FP8 128 /* fp8 forward: expert segments are padded to 128 rows */
 
@@ -138,6 +139,18 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
                            int intermediate, int local_experts, int topk, void* workspace,
                            int64_t workspace_bytes, int device, void* stream);
 
+/* The same forward with fp16 tensors (Precision.FP16, config.py:54 and 212-213;
+ * the reference checks it at atol 1e-2, reference.py:41).  Every 16-bit tensor
+ * (hidden_states, w1, w2, out) is IEEE half; accumulation stays fp32 and the
+ * intermediate activation and the per-assignment rows are rounded to half where
+ * the bf16 forward rounds to bf16.  Workspace: mb200_workspace_bytes with
+ * MB200_PRECISION_FP16 (the same size as bf16). */
+int mb200_moe_forward_fp16(const void* hidden_states, const void* w1, const void* w2,
+                           const int32_t* topk_ids, const float* topk_weights,
+                           const int32_t* expert_map, void* out, int64_t tokens, int hidden,
+                           int intermediate, int local_experts, int topk, void* workspace,
+                           int64_t workspace_bytes, int device, void* stream);
+
 /* fp8 counterpart of mb200_grouped_gemm_bf16 (reference.py:65-95 block matmul), on
  * a schedule padded to MB200_PAD_ROWS_FP8.
  * a: e4m3 [row_capacity, K] sorted rows; a_scale_t: fp32 [K/128][row_capacity]
@@ -181,6 +194,8 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
  *   expert_parallel = 0  tensor parallel: all experts, intermediate/world columns
  * Every rank passes its own token shard (hidden_states [tokens, hidden], routing
  * over GLOBAL expert ids) and receives its own rows of the combined output.
+ * precision: MB200_PRECISION_BF16, _FP8 (bf16 tokens and output, e4m3 weights
+ * with scales) or _FP16 (half tokens, weights and output; scales unused).
  *
  * symmetric_ptrs[world]: base pointers, valid in THIS process, of one buffer per
  * rank with mb200_dist_symmetric_bytes() bytes, 1024-byte aligned, zero-filled

@@ -16,9 +16,10 @@ import torch
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libmoe_bench_b200.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 PRECISION_BF16 = 0
 PRECISION_FP8 = 1
+PRECISION_FP16 = 2
 PAD_ROWS_BF16 = 16
 PAD_ROWS_FP8 = 128
 
@@ -40,6 +41,10 @@ SIGNATURES = {
     ),
     "mb200_workspace_bytes": (c_i64, [c_i32, c_i64, c_i32, c_i32, c_i32, c_i32]),
     "mb200_moe_forward_bf16": (
+        c_i32,
+        [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64, c_i32, c_vp],
+    ),
+    "mb200_moe_forward_fp16": (
         c_i32,
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64, c_i32, c_vp],
     ),
@@ -226,12 +231,16 @@ def grouped_gemm_bf16(mode, a, w, hidden, intermediate, counts, prefix, sorted_i
 
 
 def moe_forward_bf16(x, w1, w2, topk_ids, topk_weights, expert_map, out, workspace):
-    """Enqueue the bf16 layer forward on the current stream."""
+    """Enqueue the 16-bit layer forward on the current stream: bf16 tensors, or
+    fp16 when ``x`` is ``torch.float16`` (weights and output must match)."""
     t, hidden = x.shape
     e_local, two_n, _ = w1.shape
     dev = x.device
+    if not (x.dtype == w1.dtype == w2.dtype == out.dtype) or x.dtype not in (torch.bfloat16, torch.float16):
+        raise MB200Error(f"moe_forward: tensors must all be bf16 or all fp16, got {x.dtype}/{w1.dtype}/{w2.dtype}/{out.dtype}")
+    fn = load().mb200_moe_forward_fp16 if x.dtype == torch.float16 else load().mb200_moe_forward_bf16
     _check(
-        load().mb200_moe_forward_bf16(
+        fn(
             _ptr(x), _ptr(w1), _ptr(w2), _ptr(topk_ids), _ptr(topk_weights), _ptr(expert_map), _ptr(out),
             t, hidden, two_n // 2, e_local, topk_ids.shape[1], _ptr(workspace), workspace.numel(),
             dev.index or 0, _stream(dev),

@@ -52,7 +52,7 @@ EncodeTiledFn encode_tiled_fn() {
 }  // namespace
 
 int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows,
-                       uint64_t cols, uint32_t box_rows) {
+                       uint64_t cols, uint32_t box_rows, int fp16) {
   EncodeTiledFn fn = encode_tiled_fn();
   MB200_REQUIRE(fn != nullptr, kDriverEntryMissing, "cuTensorMapEncodeTiled is not available");
   MB200_REQUIRE(elem_bytes == 1 || elem_bytes == 2, kInvalidArgument, "tensor map: element size %d", elem_bytes);
@@ -66,8 +66,10 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint6
   const cuuint64_t strides[1] = {cols * elem_bytes};
   const cuuint32_t box[2] = {uint32_t(128 / elem_bytes), box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
-                  2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const CUtensorMapDataType dtype = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                    : fp16          ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   MB200_REQUIRE(r == CUDA_SUCCESS, kCudaError, "cuTensorMapEncodeTiled failed with code %d", int(r));
@@ -132,11 +134,12 @@ int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts,
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
-                   unsigned long long* clock_probe, const FusedDispatch* dispatch) {
+                   unsigned long long* clock_probe, const FusedDispatch* dispatch, int fp16) {
   CUtensorMap map_w;
   TokenMaps maps_t;
   GemmArgs g{};
   g.clock_probe = clock_probe;
+  g.fp16 = fp16;
   g.counts = counts;
   g.mtile_prefix = prefix;
   g.sorted_ids = sorted;
@@ -147,16 +150,16 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
   int rc;
   const int token_cols = mode == kGateUpSwiglu ? hidden : intermediate;
   for (int i = 0; i < kTokenBoxes; ++i)
-    if ((rc = make_tensor_map_2d(&maps_t.m[i], a, 2, uint64_t(cap), uint64_t(token_cols), 16u << i))) return rc;
+    if ((rc = make_tensor_map_2d(&maps_t.m[i], a, 2, uint64_t(cap), uint64_t(token_cols), 16u << i, fp16))) return rc;
   if (mode == kGateUpSwiglu) {
-    if ((rc = make_tensor_map_2d(&map_w, w, 2, uint64_t(local_experts) * 2 * intermediate, uint64_t(hidden), 128))) return rc;
+    if ((rc = make_tensor_map_2d(&map_w, w, 2, uint64_t(local_experts) * 2 * intermediate, uint64_t(hidden), 128, fp16))) return rc;
     g.n_tiles = (intermediate + 127) / 128;
     g.k_iters = (hidden + 63) / 64;
     g.b_rows_per_expert = 2 * intermediate;
     g.b_half_offset = intermediate;
     g.out_cols = intermediate;
   } else {
-    if ((rc = make_tensor_map_2d(&map_w, w, 2, uint64_t(local_experts) * hidden, uint64_t(intermediate), 256))) return rc;
+    if ((rc = make_tensor_map_2d(&map_w, w, 2, uint64_t(local_experts) * hidden, uint64_t(intermediate), 256, fp16))) return rc;
     g.n_tiles = (hidden + 255) / 256;
     g.k_iters = (intermediate + 63) / 64;
     g.b_rows_per_expert = hidden;
@@ -293,7 +296,7 @@ int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_cap, const void
 int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
                               int local_experts, int topk) {
   if (check_shape(tokens, hidden, intermediate, local_experts, topk)) return -1;
-  if (precision != MB200_PRECISION_BF16 && precision != MB200_PRECISION_FP8) {
+  if (precision != MB200_PRECISION_BF16 && precision != MB200_PRECISION_FP8 && precision != MB200_PRECISION_FP16) {
     set_last_error("workspace_bytes: unknown precision %d", precision);
     return -1;
   }
@@ -302,21 +305,21 @@ int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int int
   return make_layout(precision, tokens, hidden, intermediate, local_experts, topk, pad_rows_of(precision)).total;
 }
 
-int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void* w2,
-                           const int32_t* topk_ids, const float* topk_weights,
-                           const int32_t* expert_map, void* out, int64_t tokens, int hidden,
-                           int intermediate, int local_experts, int topk, void* workspace,
-                           int64_t workspace_bytes, int device, void* stream) {
+static int moe_forward_16bit(int fp16, const void* hidden_states, const void* w1, const void* w2,
+                             const int32_t* topk_ids, const float* topk_weights,
+                             const int32_t* expert_map, void* out, int64_t tokens, int hidden,
+                             int intermediate, int local_experts, int topk, void* workspace,
+                             int64_t workspace_bytes, int device, void* stream) {
   int rc = check_shape(tokens, hidden, intermediate, local_experts, topk);
   if (rc) return rc;
   if (tokens == 0) return kOk;
   MB200_REQUIRE(hidden_states && w1 && w2 && topk_ids && topk_weights && out && workspace, kInvalidArgument,
-                "moe_forward_bf16: null pointer");
+                "moe_forward (16-bit): null pointer");
   const Layout l = make_layout(MB200_PRECISION_BF16, tokens, hidden, intermediate, local_experts, topk, kPadBf16);
-  MB200_REQUIRE(workspace_bytes >= l.total, kWorkspaceTooSmall, "moe_forward_bf16: workspace %lld < %lld bytes",
+  MB200_REQUIRE(workspace_bytes >= l.total, kWorkspaceTooSmall, "moe_forward (16-bit): workspace %lld < %lld bytes",
                 (long long)workspace_bytes, (long long)l.total);
   MB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, kInvalidArgument,
-                "moe_forward_bf16: workspace must be 1024-byte aligned");
+                "moe_forward (16-bit): workspace must be 1024-byte aligned");
   cudaStream_t s = as_stream(stream);
   char* ws = reinterpret_cast<char*>(workspace);
   int* status = reinterpret_cast<int*>(ws + l.status);
@@ -346,15 +349,33 @@ int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void
   mark_stage(2, s);
   if ((rc = run_gemm_stage(kGateUpSwiglu, xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, nullptr, act, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8), &disp))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 8), &disp, fp16))) return rc;
   mark_stage(3, s);
   if ((rc = run_gemm_stage(kDownWeighted, act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 12)))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16))) return rc;
   mark_stage(4, s);
-  rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s);
+  rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s, fp16);
   mark_stage(5, s);
   return rc;
+}
+
+int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void* w2,
+                           const int32_t* topk_ids, const float* topk_weights,
+                           const int32_t* expert_map, void* out, int64_t tokens, int hidden,
+                           int intermediate, int local_experts, int topk, void* workspace,
+                           int64_t workspace_bytes, int device, void* stream) {
+  return moe_forward_16bit(0, hidden_states, w1, w2, topk_ids, topk_weights, expert_map, out, tokens, hidden,
+                           intermediate, local_experts, topk, workspace, workspace_bytes, device, stream);
+}
+
+int mb200_moe_forward_fp16(const void* hidden_states, const void* w1, const void* w2,
+                           const int32_t* topk_ids, const float* topk_weights,
+                           const int32_t* expert_map, void* out, int64_t tokens, int hidden,
+                           int intermediate, int local_experts, int topk, void* workspace,
+                           int64_t workspace_bytes, int device, void* stream) {
+  return moe_forward_16bit(1, hidden_states, w1, w2, topk_ids, topk_weights, expert_map, out, tokens, hidden,
+                           intermediate, local_experts, topk, workspace, workspace_bytes, device, stream);
 }
 
 int mb200_grouped_gemm_fp8(int mode, const void* a, const float* a_scale_t, int64_t row_cap, const void* w,

@@ -4,6 +4,7 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -63,6 +64,39 @@ __device__ __forceinline__ bool elect_one() {
       "}\n"
       : "=r"(pred));
   return pred != 0;
+}
+
+// ---- 16-bit activations: bf16 or fp16, chosen at run time (a warp-uniform flag) ----
+__device__ __forceinline__ uint16_t to_h16(float v, int fp16) {
+  if (fp16) return __half_as_ushort(__float2half_rn(v));
+  return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ void add_h16x8(const uint4& v, float (&acc)[8], int fp16) {
+  if (fp16) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      acc[2 * i] += f.x;
+      acc[2 * i + 1] += f.y;
+    }
+  } else {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      acc[2 * i] += f.x;
+      acc[2 * i + 1] += f.y;
+    }
+  }
+}
+__device__ __forceinline__ uint4 pack_h16x8(const float (&acc)[8], int fp16) {
+  uint4 o;
+  uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    w[k] = uint32_t(to_h16(acc[2 * k], fp16)) | (uint32_t(to_h16(acc[2 * k + 1], fp16)) << 16);
+  return o;
 }
 
 // ---- mbarrier -----------------------------------------------------------------

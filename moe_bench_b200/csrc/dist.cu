@@ -89,8 +89,10 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
                        int global_experts, int topk, int rank, int world, void* const* symmetric_ptrs,
                        int64_t symmetric_bytes, uint32_t seq_base, void* workspace, int64_t workspace_bytes,
                        int device, void* stream) {
-  MB200_REQUIRE(precision == MB200_PRECISION_BF16 || precision == MB200_PRECISION_FP8, kInvalidArgument,
-                "dist_forward: unknown precision %d", precision);
+  MB200_REQUIRE(precision == MB200_PRECISION_BF16 || precision == MB200_PRECISION_FP8 ||
+                    precision == MB200_PRECISION_FP16,
+                kInvalidArgument, "dist_forward: unknown precision %d", precision);
+  const int fp16 = precision == MB200_PRECISION_FP16;
   MB200_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, kInvalidArgument,
                 "dist_forward: rank %d of %d (at most %d ranks)", rank, world, kMaxPeers);
   const bool fp8 = precision == MB200_PRECISION_FP8;
@@ -224,20 +226,20 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   } else {
     if ((rc = run_gemm_stage(kGateUpSwiglu, ws + l.xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, nullptr, ws + l.act, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8), &disp))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 8), &disp, fp16))) return rc;
     mark_stage(3, s);
     if ((rc = run_gemm_stage(kDownWeighted, ws + l.act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, weights_all, y, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 12)))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16))) return rc;
   }
   mark_stage(4, s);
   if ((rc = launch_combine_bf16(y, sched.inverse, int(all_tokens), topk, hidden,
-                                reinterpret_cast<__nv_bfloat16*>(sym + sl.partial), s))) return rc;
+                                reinterpret_cast<__nv_bfloat16*>(sym + sl.partial), s, fp16))) return rc;
   // 5. combine across ranks
   if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 2, status, s))) return rc;
   if ((rc = launch_reduce_partials(offset_table(symmetric_ptrs, world, sl.partial), rank, world, int(tokens), topk,
                                    topk_ids, expert_parallel ? local_experts : 0, hidden,
-                                   reinterpret_cast<__nv_bfloat16*>(out), s))) return rc;
+                                   reinterpret_cast<__nv_bfloat16*>(out), s, fp16))) return rc;
   // peers may still be reading this rank's buffers: nobody restages before all are done
   rc = launch_peer_barrier(flags, rank, world, seq_base + 3, status, s);
   mark_stage(5, s);

@@ -1,4 +1,4 @@
-// Grouped per-expert bf16 GEMMs of the MoE layer on the sm_100a tensor cores.
+// Grouped per-expert 16-bit (bf16 or fp16) GEMMs of the MoE layer on the sm_100a tensor cores.
 //
 // Orientation: the WEIGHT rows sit on the accumulator rows (tensor-memory lanes,
 // MMA M = 128) and the TOKENS on the accumulator columns (MMA N, any multiple of
@@ -294,7 +294,8 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       tc_fence_after();
       const uint32_t d0 = tmem_base + buf * 256;
       const uint32_t d1 = d0 + acc1_off;
-      const uint32_t idesc = make_idesc(1, 1, 128, uint32_t(tc.ntok));
+      const uint32_t fmt = args.fp16 ? 0u : 1u;  // kind::f16 operand format: 0 = f16, 1 = bf16
+      const uint32_t idesc = make_idesc(fmt, fmt, 128, uint32_t(tc.ntok));
       for (int kb = 0; kb < args.k_iters; ++kb) {
         ok = mbar_wait(smem_u32(&tail->full[stage]), phase, ctx, 3);
         if (!ok) break;
@@ -389,7 +390,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       tc_fence_after();
       const uint32_t t0 = tmem_base + buf * 256 + (uint32_t(quarter * 32) << 16);
       const uint32_t t1 = t0 + acc1_off;
-      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(args.out);
+      uint16_t* out = reinterpret_cast<uint16_t*>(args.out);
       const int chunks = tc.ntok >> 4;
 
       if (kMode == kGateUpSwiglu) {
@@ -401,12 +402,12 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
           tmem_ld16(t1 + c * 16, u);
           tmem_ld_wait();
           if (f_ok) {
-            __nv_bfloat16* dst = out + size_t(tc.row0 + c * 16) * args.out_cols + feature;
+            uint16_t* dst = out + size_t(tc.row0 + c * 16) * args.out_cols + feature;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               if (c * 16 + j < tc.valid)
                 dst[size_t(j) * args.out_cols] =
-                    __float2bfloat16_rn(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])));
+                    to_h16(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])), args.fp16);
             }
           }
         }
@@ -422,9 +423,9 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
             const int a = tail->tile_assign[par][c * 16 + j];
             if (a >= 0) {
               const float w = tail->tile_weight[par][c * 16 + j];
-              __nv_bfloat16* dst = out + size_t(a) * args.out_cols + feature;
-              if (feature < args.out_cols) dst[0] = __float2bfloat16_rn(w * __uint_as_float(v0[j]));
-              if (feature + 128 < args.out_cols) dst[128] = __float2bfloat16_rn(w * __uint_as_float(v1[j]));
+              uint16_t* dst = out + size_t(a) * args.out_cols + feature;
+              if (feature < args.out_cols) dst[0] = to_h16(w * __uint_as_float(v0[j]), args.fp16);
+              if (feature + 128 < args.out_cols) dst[128] = to_h16(w * __uint_as_float(v1[j]), args.fp16);
             }
           }
         }

@@ -35,8 +35,9 @@ int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map
                  cudaStream_t stream);
 
 // ---- rows.cu ------------------------------------------------------------------------
+// y and out are 16-bit (bf16, or fp16 when fp16 != 0); fp32 sum.
 int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, int topk,
-                        int hidden, __nv_bfloat16* out, cudaStream_t stream);
+                        int hidden, __nv_bfloat16* out, cudaStream_t stream, int fp16 = 0);
 // Per-row, per-128-group e4m3 quantisation.  scales_t is [K/128][scale_ld] (group-major).
 int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uint8_t* q,
                            float* scales, int64_t scale_ld, int transposed, cudaStream_t stream);
@@ -60,6 +61,7 @@ struct GemmArgs {
   const float* row_scale;  // per-assignment combine weight (second GEMM)
   int* status;
   unsigned long long* clock_probe;  // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel
+  int fp16;                // operands and outputs are fp16 instead of bf16
 };
 enum GemmMode : int { kGateUpSwiglu = 0, kDownWeighted = 1 };
 // Dispatch fused into the gate/up GEMM: extra warps of every CTA fill the sorted
@@ -131,7 +133,7 @@ int launch_gather_rows_peer_fp8(const PeerTable& x, const PeerTable& xs, int ran
                                 float* out_scales_t, int64_t row_capacity, cudaStream_t stream);
 int launch_reduce_partials(const PeerTable& partial, int rank, int world, int tokens, int topk,
                            const int* topk_ids, int experts_per_rank, int hidden, __nv_bfloat16* out,
-                           cudaStream_t stream);
+                           cudaStream_t stream, int fp16 = 0);
 
 // ---- api.cu helpers shared with dist.cu -----------------------------------------------------
 struct Layout {
@@ -144,12 +146,14 @@ Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, 
                    int pad_rows);
 int64_t row_capacity(int64_t tokens, int topk, int local_experts, int pad_rows);
 inline int pad_rows_of(int precision) { return precision == 1 /* fp8 */ ? kTileM : kPadBf16; }
+inline int elem_bytes_of(int precision) { return precision == 1 /* fp8 */ ? 1 : 2; }
 int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts, int topk);
 int check_shape_fp8(int hidden, int intermediate);
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
-                   unsigned long long* clock_probe = nullptr, const FusedDispatch* dispatch = nullptr);
+                   unsigned long long* clock_probe = nullptr, const FusedDispatch* dispatch = nullptr,
+                   int fp16 = 0);
 int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,
@@ -161,6 +165,6 @@ void mark_stage(int i, cudaStream_t s);
 // Row-major 2-D tensor [rows][cols] of elem_bytes elements, boxes of
 // box_rows x (128 bytes of columns), 128-byte swizzle.
 int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows,
-                       uint64_t cols, uint32_t box_rows);
+                       uint64_t cols, uint32_t box_rows, int fp16 = 0);
 
 }  // namespace mb200

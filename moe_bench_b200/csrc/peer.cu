@@ -116,22 +116,12 @@ __global__ void gather_rows_peer_fp8_kernel(PeerTable xq, PeerTable xs, int rank
   }
 }
 
-__device__ __forceinline__ void add_bf16x8(const uint4& v, float (&acc)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __bfloat1622float2(h[i]);
-    acc[2 * i] += f.x;
-    acc[2 * i + 1] += f.y;
-  }
-}
-
 // out[t] = sum over ranks p (ascending) of partial_p[ring(p)*T + t], ring(p) =
 // (rank - p) mod world.  experts_per_rank > 0 (EP): only ranks that own one of
 // the token's experts are read; 0 (TP): every rank contributes.
 __global__ void reduce_partials_kernel(PeerTable partial, int rank, int world, int tokens, int topk,
                                        const int* __restrict__ topk_ids, int experts_per_rank,
-                                       int vec_per_row, uint4* __restrict__ out) {
+                                       int vec_per_row, uint4* __restrict__ out, int fp16) {
   const int64_t total = int64_t(tokens) * vec_per_row;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += int64_t(gridDim.x) * blockDim.x) {
@@ -151,13 +141,9 @@ __global__ void reduce_partials_kernel(PeerTable partial, int rank, int world, i
       const int ring = (rank - p + world) % world;
       const uint4* src = reinterpret_cast<const uint4*>(partial.ptr[p]) +
                          (int64_t(ring) * tokens + t) * vec_per_row + v;
-      add_bf16x8(*src, acc);
+      add_h16x8(*src, acc, fp16);
     }
-    uint4 o;
-    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
-    out[i] = o;
+    out[i] = pack_h16x8(acc, fp16);
   }
 }
 
@@ -217,11 +203,11 @@ int launch_gather_rows_peer_fp8(const PeerTable& x, const PeerTable& xs, int ran
 
 int launch_reduce_partials(const PeerTable& partial, int rank, int world, int tokens, int topk,
                            const int* topk_ids, int experts_per_rank, int hidden, __nv_bfloat16* out,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, int fp16) {
   MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "reduce: hidden=%d must be a multiple of 8", hidden);
   const int threads = 256;
   reduce_partials_kernel<<<grid_for_rows(int64_t(tokens) * (hidden / 8), threads, 16), threads, 0, stream>>>(
-      partial, rank, world, tokens, topk, topk_ids, experts_per_rank, hidden / 8, reinterpret_cast<uint4*>(out));
+      partial, rank, world, tokens, topk, topk_ids, experts_per_rank, hidden / 8, reinterpret_cast<uint4*>(out), fp16);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

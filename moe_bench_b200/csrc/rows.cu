@@ -17,18 +17,8 @@ namespace mb200 {
 
 namespace {
 
-__device__ __forceinline__ void accumulate_bf16x8(const uint4& v, float (&acc)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __bfloat1622float2(h[i]);
-    acc[2 * i] += f.x;
-    acc[2 * i + 1] += f.y;
-  }
-}
-
 __global__ void combine_bf16_kernel(const uint4* __restrict__ y, const int* __restrict__ inverse,
-                                    int tokens, int topk, int vec_per_row, uint4* __restrict__ out) {
+                                    int tokens, int topk, int vec_per_row, uint4* __restrict__ out, int fp16) {
   const int64_t total = int64_t(tokens) * vec_per_row;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += int64_t(gridDim.x) * blockDim.x) {
@@ -38,13 +28,9 @@ __global__ void combine_bf16_kernel(const uint4* __restrict__ y, const int* __re
     for (int j = 0; j < topk; ++j) {
       const int64_t n = t * topk + j;
       if (__ldg(inverse + n) < 0) continue;  // expert on another rank: contributes zero
-      accumulate_bf16x8(__ldg(y + n * vec_per_row + v), acc);
+      add_h16x8(__ldg(y + n * vec_per_row + v), acc, fp16);
     }
-    uint4 o;
-    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
-    out[i] = o;
+    out[i] = pack_h16x8(acc, fp16);
   }
 }
 
@@ -157,13 +143,13 @@ int sm_count() {
 }  // namespace
 
 int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, int topk, int hidden,
-                        __nv_bfloat16* out, cudaStream_t stream) {
+                        __nv_bfloat16* out, cudaStream_t stream, int fp16) {
   MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "combine: hidden=%d must be a multiple of 8", hidden);
   if (tokens == 0) return kOk;
   const int threads = 256;
   const int blocks = grid_for(int64_t(tokens) * (hidden / 8), threads, sm_count(), 16);
   combine_bf16_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(y), inverse, tokens,
-                                                     topk, hidden / 8, reinterpret_cast<uint4*>(out));
+                                                     topk, hidden / 8, reinterpret_cast<uint4*>(out), fp16);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -63,9 +63,12 @@ class B200FusedExperts(MoEImplementation):
         if not problem.hidden_states.is_cuda:
             raise capi.MB200Error("B200FusedExperts needs CUDA tensors; there is no CPU path")
         prec = Precision(problem.config.precision.value)
-        if prec == Precision.FP16:
-            raise capi.MB200Error("precision fp16 is not built in this library version (bf16 and fp8 are)")
         self._fp8 = prec == Precision.FP8
+        self._dtype = torch.float16 if prec == Precision.FP16 else torch.bfloat16
+        if not self._fp8 and problem.w1.dtype != self._dtype:
+            raise capi.MB200Error(f"{prec.value} problem with {problem.w1.dtype} weights")
+        if problem.hidden_states.dtype != self._dtype:
+            raise capi.MB200Error(f"{prec.value} problem with {problem.hidden_states.dtype} hidden_states")
         if self._fp8:
             qc = problem.quant_config
             if qc is None or qc.w1_scale is None or qc.w2_scale is None:
@@ -81,9 +84,9 @@ class B200FusedExperts(MoEImplementation):
         t, hidden = problem.hidden_states.shape
         e_local, two_n, _ = problem.w1.shape
         topk = problem.topk_ids.shape[1]
-        nbytes = capi.workspace_bytes(
-            capi.PRECISION_FP8 if self._fp8 else capi.PRECISION_BF16, t, hidden, two_n // 2, e_local, topk
-        )
+        code = {Precision.BF16: capi.PRECISION_BF16, Precision.FP8: capi.PRECISION_FP8,
+                Precision.FP16: capi.PRECISION_FP16}[prec]
+        nbytes = capi.workspace_bytes(code, t, hidden, two_n // 2, e_local, topk)
         dev = problem.hidden_states.device
         # torch's caching allocator hands out 512-byte aligned blocks; over-allocate
         # and slice to the 1024-byte boundary the tile buffers need.
@@ -91,7 +94,7 @@ class B200FusedExperts(MoEImplementation):
         shift = (-raw.data_ptr()) % 1024
         self._workspace = raw[shift : shift + nbytes]
         self._workspace[:256].zero_()  # status word
-        self._out = torch.empty(t, hidden, dtype=torch.bfloat16, device=dev)
+        self._out = torch.empty(t, hidden, dtype=self._dtype, device=dev)
         self._key = self._shape_key(problem)
 
     def run(self, problem: MoEProblem) -> torch.Tensor:

@@ -10,7 +10,7 @@ Where the reference's serial scheme all-gathers every token and reduce-scatters
 a mostly empty result (``schemes.py:117-143``), this scheme keeps each rank's
 staged tokens in a buffer all peers have mapped and lets kernels pull exactly
 the rows they need over NVLink (fp8 rows + scales for fp8 problems).  Both
-parallel modes and both precisions go through one entry point.
+parallel modes and all three precisions go through one entry point.
 """
 
 from __future__ import annotations
@@ -160,13 +160,15 @@ class B200Scheme(DistributedScheme):
             raise capi.MB200Error("B200Scheme needs CUDA tensors; there is no CPU path")
         cfg = problem.config
         prec = Precision(cfg.precision.value)
-        if prec == Precision.FP16:
-            raise capi.MB200Error("precision fp16 is not built in this library version (bf16 and fp8 are)")
         capi.load()
         self.ctx, self.problem = ctx, problem
         self._fp8 = prec == Precision.FP8
         self._ep = ParallelMode(cfg.parallel_mode.value) == ParallelMode.EP
-        self._precision = capi.PRECISION_FP8 if self._fp8 else capi.PRECISION_BF16
+        self._precision = {Precision.BF16: capi.PRECISION_BF16, Precision.FP8: capi.PRECISION_FP8,
+                           Precision.FP16: capi.PRECISION_FP16}[prec]
+        self._dtype = torch.float16 if prec == Precision.FP16 else torch.bfloat16
+        if problem.hidden_states.dtype != self._dtype:
+            raise capi.MB200Error(f"{prec.value} problem with {problem.hidden_states.dtype} hidden_states")
         self._w1_scale = self._w2_scale = None
         if self._fp8:
             qc = problem.quant_config
@@ -189,7 +191,7 @@ class B200Scheme(DistributedScheme):
         shift = (-raw.data_ptr()) % 1024
         self._workspace = raw[shift : shift + nbytes]
         self._workspace[:256].zero_()
-        self._out = torch.empty(t, hidden, dtype=torch.bfloat16, device=dev)
+        self._out = torch.empty(t, hidden, dtype=self._dtype, device=dev)
         self._hidden = problem.hidden_states.contiguous()
         self._ids = problem.topk_ids.contiguous()
         self._weights = problem.topk_weights.contiguous()

@@ -35,7 +35,7 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 
 
 def test_abi_version_and_pure_host_queries(lib):
-    assert lib.mb200_abi_version() == capi.ABI_VERSION == 2
+    assert lib.mb200_abi_version() == capi.ABI_VERSION == 3
     # 8 assignments can hit at most 8 experts: 8 + 8*127 rows, rounded to 128
     assert lib.mb200_row_capacity(1, 8, 256, 128) == 1024
     assert lib.mb200_row_capacity(1, 8, 256, 16) == 128
@@ -45,6 +45,7 @@ def test_abi_version_and_pure_host_queries(lib):
     n = lib.mb200_workspace_bytes(capi.PRECISION_BF16, 128, 7168, 2048, 256, 8)
     assert n > 128 * 8 * 7168 * 2
     assert n % 1024 == 0
+    assert lib.mb200_workspace_bytes(capi.PRECISION_FP16, 128, 7168, 2048, 256, 8) == n
 
 
 def test_argument_errors_are_reported_not_fatal(lib):

@@ -41,7 +41,7 @@ def _cfg(mode, precision, world, **kw):
 
 
 @pytest.mark.parametrize("mode", ["ep", "tp"])
-@pytest.mark.parametrize("precision", ["bf16", "fp8"])
+@pytest.mark.parametrize("precision", ["bf16", "fp8", "fp16"])
 @pytest.mark.parametrize("tokens", [1, 200])
 def test_scheme_world1(mode, precision, tokens):
     from moe_bench_b200.scheme import DistContext, get_scheme
