@@ -50,6 +50,8 @@ constexpr int kThreads = (kFirstDispatchWarp + kDispatchWarps) * 32;
 constexpr int kMaxTokens = 256;
 
 struct SmemTail {
+  // epilogue transposition scratch: per warp two [16 tokens][32 features] 16-bit blocks
+  alignas(16) uint16_t transpose[kEpilogueWarps][2][16 * 32];
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
@@ -225,8 +227,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    const CUtensorMap* map_t = &maps_t.m[geo.box_index];
-    if (lane == 0) prefetch_tmap(map_t);
+    if (lane < kTokenBoxes) prefetch_tmap(&maps_t.m[lane]);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -265,7 +266,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
           const uint32_t w_dst = ring_addr + stage * geo.stage_bytes;
           const uint32_t t_dst = w_dst + kWeightBytes;
           const int kcol = kb * 64;
-          mbar_expect_tx(bar, uint32_t(geo.stage_bytes));
+          mbar_expect_tx(bar, uint32_t(kWeightBytes + tc.ntok * 128));
           if (kMode == kGateUpSwiglu) {
             tma_load_2d(w_dst, &map_w, kcol, w_row + tc.fblock * 128, bar);
             tma_load_2d(w_dst + kWeightBytes / 2, &map_w, kcol,
@@ -273,7 +274,17 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
           } else {
             tma_load_2d(w_dst, &map_w, kcol, w_row + tc.fblock * 256, bar);
           }
-          tma_load_2d(t_dst, map_t, kcol, tc.row0, bar);
+          // exactly ntok token rows: one box per set bit of ntok/16 (largest first), so a
+          // 144-token tile moves 18 KB of tokens, not the 32 KB of the launch's largest box
+          const int nb16 = tc.ntok >> 4;
+          int r = 0;
+#pragma unroll
+          for (int b = kTokenBoxes - 1; b >= 0; --b) {
+            if (nb16 & (1 << b)) {
+              tma_load_2d(t_dst + uint32_t(r) * 128u, &maps_t.m[b], kcol, tc.row0 + r, bar);
+              r += 16 << b;
+            }
+          }
         }
         __syncwarp();
         if (++stage == geo.stages) { stage = 0; phase ^= 1; }
@@ -285,11 +296,20 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     uint32_t phase = 0;
     uint32_t it = 0;
     bool ok = true;
+#ifdef MB200_PROBE_WAITS
+    long long wait_full = 0, wait_acc = 0, c_start = clock64();
+#endif
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
       const TileCoord tc = decode_tile(tile, tail, args.counts, E, args.n_tiles, geo.tb_rows);
       const uint32_t buf = geo.acc_bufs == 2 ? (it & 1) : 0;
       const uint32_t use = geo.acc_bufs == 2 ? (it >> 1) : it;
+#ifdef MB200_PROBE_WAITS
+      long long c_a = clock64();
+#endif
       ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), (use & 1) ^ 1, ctx, 2);
+#ifdef MB200_PROBE_WAITS
+      wait_acc += clock64() - c_a;
+#endif
       if (!ok) break;
       tc_fence_after();
       const uint32_t d0 = tmem_base + buf * 256;
@@ -297,7 +317,13 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       const uint32_t fmt = args.fp16 ? 0u : 1u;  // kind::f16 operand format: 0 = f16, 1 = bf16
       const uint32_t idesc = make_idesc(fmt, fmt, 128, uint32_t(tc.ntok));
       for (int kb = 0; kb < args.k_iters; ++kb) {
+#ifdef MB200_PROBE_WAITS
+        long long c_f = clock64();
+#endif
         ok = mbar_wait(smem_u32(&tail->full[stage]), phase, ctx, 3);
+#ifdef MB200_PROBE_WAITS
+        wait_full += clock64() - c_f;
+#endif
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
@@ -320,6 +346,14 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       if (ok && lane == 0) tc_commit(smem_u32(&tail->acc_full[buf]));
       __syncwarp();
     }
+#ifdef MB200_PROBE_WAITS
+    // diagnostic build only: cycles the MMA warp of CTA 0 waited for data / for a free accumulator
+    if (lane == 0 && blockIdx.x == 0 && args.clock_probe) {
+      args.clock_probe[4 + 3 * kMode] = wait_full;
+      args.clock_probe[5 + 3 * kMode] = wait_acc;
+      args.clock_probe[6 + 3 * kMode] = clock64() - c_start;
+    }
+#endif
   } else if (warp >= kFirstDispatchWarp) {
     // ---------------- fused dispatch (gate/up GEMM): fill the sorted row buffer ----------------
     if (kMode == kGateUpSwiglu && disp.enabled) {
@@ -360,7 +394,6 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     const int ew = warp - kFirstEpilogueWarp;
     const int quarter = warp & 3;     // tensor-memory lanes 32*quarter .. +31
     const int cgroup = ew >> 2;       // which 16-column chunks this warp takes (even / odd)
-    const int r = quarter * 32 + lane;
     const int etid = threadIdx.x - kFirstEpilogueWarp * 32;
     uint32_t it = 0;
     uint32_t epi_phase = 0;
@@ -393,46 +426,77 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       uint16_t* out = reinterpret_cast<uint16_t*>(args.out);
       const int chunks = tc.ntok >> 4;
 
+      // A thread holds one feature (accumulator row) of 16 tokens; memory wants the
+      // features of a token side by side.  Each 16-token chunk is rounded, transposed
+      // through a 1 KiB per-warp block of shared memory and leaves as 16-byte stores
+      // (8 features of one token per thread), two per thread and output block.
+      uint16_t* sc0 = tail->transpose[ew][0];
+      uint16_t* sc1 = tail->transpose[ew][1];
+      bool released = false;
+      auto release = [&]() {
+        // every value of this warp's share is in registers: the accumulator may be overwritten
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tail->acc_empty[buf]));
+        released = true;
+      };
       if (kMode == kGateUpSwiglu) {
-        const int feature = tc.fblock * 128 + r;
-        const bool f_ok = feature < args.out_cols;
+        const int feat_base = tc.fblock * 128 + quarter * 32;
         for (int c = cgroup; c < chunks; c += 2) {
           uint32_t g[16], u[16];
           tmem_ld16(t0 + c * 16, g);
           tmem_ld16(t1 + c * 16, u);
           tmem_ld_wait();
-          if (f_ok) {
-            uint16_t* dst = out + size_t(tc.row0 + c * 16) * args.out_cols + feature;
+          if (c + 2 >= chunks) release();
+          if (c * 16 >= tc.valid) continue;  // padding rows only
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (c * 16 + j < tc.valid)
-                dst[size_t(j) * args.out_cols] =
-                    to_h16(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])), args.fp16);
-            }
+          for (int j = 0; j < 16; ++j)
+            sc0[j * 32 + lane] = to_h16(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])), args.fp16);
+          __syncwarp();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int piece = lane + 32 * h;  // token piece>>2 of the chunk, features 8*(piece&3) .. +7
+            const int token = c * 16 + (piece >> 2);
+            const int feat = feat_base + (piece & 3) * 8;
+            if (token < tc.valid && feat < args.out_cols)
+              *reinterpret_cast<uint4*>(out + size_t(tc.row0 + token) * args.out_cols + feat) =
+                  *reinterpret_cast<const uint4*>(sc0 + piece * 8);
           }
+          __syncwarp();
         }
       } else {
-        const int feature = tc.fblock * 256 + r;
+        const int feat_base = tc.fblock * 256 + quarter * 32;
         for (int c = cgroup; c < chunks; c += 2) {
           uint32_t v0[16], v1[16];
           tmem_ld16(t0 + c * 16, v0);
           tmem_ld16(t1 + c * 16, v1);
           tmem_ld_wait();
+          if (c + 2 >= chunks) release();
+          if (c * 16 >= tc.valid) continue;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int a = tail->tile_assign[par][c * 16 + j];
+            const float w = tail->tile_weight[par][c * 16 + j];
+            sc0[j * 32 + lane] = to_h16(w * __uint_as_float(v0[j]), args.fp16);
+            sc1[j * 32 + lane] = to_h16(w * __uint_as_float(v1[j]), args.fp16);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int piece = lane + 32 * h;
+            const int a = tail->tile_assign[par][c * 16 + (piece >> 2)];
+            const int feat = feat_base + (piece & 3) * 8;
             if (a >= 0) {
-              const float w = tail->tile_weight[par][c * 16 + j];
-              uint16_t* dst = out + size_t(a) * args.out_cols + feature;
-              if (feature < args.out_cols) dst[0] = to_h16(w * __uint_as_float(v0[j]), args.fp16);
-              if (feature + 128 < args.out_cols) dst[128] = to_h16(w * __uint_as_float(v1[j]), args.fp16);
+              uint16_t* dst = out + size_t(a) * args.out_cols + feat;
+              if (feat < args.out_cols)
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(sc0 + piece * 8);
+              if (feat + 128 < args.out_cols)
+                *reinterpret_cast<uint4*>(dst + 128) = *reinterpret_cast<const uint4*>(sc1 + piece * 8);
             }
           }
+          __syncwarp();
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&tail->acc_empty[buf]));
+      if (!released) release();
     }
   }
 
@@ -464,6 +528,8 @@ int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const Toke
                 "grouped_gemm: %d local experts, supported 1..%d", args.num_experts, kMaxExperts);
   MB200_REQUIRE(!dispatch.enabled || mode == kGateUpSwiglu, kInvalidArgument,
                 "grouped_gemm: fused dispatch belongs to the gate/up stage");
+  MB200_REQUIRE((reinterpret_cast<uintptr_t>(args.out) & 15) == 0 && args.out_cols % 8 == 0, kInvalidArgument,
+                "grouped_gemm: output must be 16-byte aligned with a row length that is a multiple of 8");
   static bool configured[64][2] = {};
   int sms = 0;
   MB200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
