@@ -137,7 +137,8 @@ __device__ __forceinline__ bool epilogue_barrier(uint64_t* bar, uint32_t& phase,
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
-  return g / (1.0f + __expf(-g)) * u;
+  // fast reciprocal: ~2 ulp, far inside the 16-bit rounding of the result
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
 template <int kMode>
@@ -442,13 +443,8 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       };
       if (kMode == kGateUpSwiglu) {
         const int feat_base = tc.fblock * 128 + quarter * 32;
-        for (int c = cgroup; c < chunks; c += 2) {
-          uint32_t g[16], u[16];
-          tmem_ld16(t0 + c * 16, g);
-          tmem_ld16(t1 + c * 16, u);
-          tmem_ld_wait();
-          if (c + 2 >= chunks) release();
-          if (c * 16 >= tc.valid) continue;  // padding rows only
+        auto emit = [&](int c, const uint32_t (&g)[16], const uint32_t (&u)[16]) {
+          if (c * 16 >= tc.valid) return;  // padding rows only
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             sc0[j * 32 + lane] = to_h16(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])), args.fp16);
@@ -463,16 +459,26 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
                   *reinterpret_cast<const uint4*>(sc0 + piece * 8);
           }
           __syncwarp();
+        };
+        // two chunks per tensor-memory round trip
+        for (int c = cgroup; c < chunks; c += 4) {
+          uint32_t ga[16], ua[16], gb[16], ub[16];
+          const bool two = c + 2 < chunks;
+          tmem_ld16(t0 + c * 16, ga);
+          tmem_ld16(t1 + c * 16, ua);
+          if (two) {
+            tmem_ld16(t0 + (c + 2) * 16, gb);
+            tmem_ld16(t1 + (c + 2) * 16, ub);
+          }
+          tmem_ld_wait();
+          if (c + 4 >= chunks) release();
+          emit(c, ga, ua);
+          if (two) emit(c + 2, gb, ub);
         }
       } else {
         const int feat_base = tc.fblock * 256 + quarter * 32;
-        for (int c = cgroup; c < chunks; c += 2) {
-          uint32_t v0[16], v1[16];
-          tmem_ld16(t0 + c * 16, v0);
-          tmem_ld16(t1 + c * 16, v1);
-          tmem_ld_wait();
-          if (c + 2 >= chunks) release();
-          if (c * 16 >= tc.valid) continue;
+        auto emit = [&](int c, const uint32_t (&v0)[16], const uint32_t (&v1)[16]) {
+          if (c * 16 >= tc.valid) return;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float w = tail->tile_weight[par][c * 16 + j];
@@ -494,6 +500,20 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
             }
           }
           __syncwarp();
+        };
+        for (int c = cgroup; c < chunks; c += 4) {
+          uint32_t a0[16], a1[16], b0[16], b1[16];
+          const bool two = c + 2 < chunks;
+          tmem_ld16(t0 + c * 16, a0);
+          tmem_ld16(t1 + c * 16, a1);
+          if (two) {
+            tmem_ld16(t0 + (c + 2) * 16, b0);
+            tmem_ld16(t1 + (c + 2) * 16, b1);
+          }
+          tmem_ld_wait();
+          if (c + 4 >= chunks) release();
+          emit(c, a0, a1);
+          if (two) emit(c + 2, b0, b1);
         }
       }
       if (!released) release();
