@@ -5,6 +5,8 @@
 #include <cstdio>
 
 #include "../../include/moe_bench_b200.h"
+#include <cstdlib>
+
 #include "layer.cuh"
 
 namespace mb200 {
@@ -134,7 +136,13 @@ int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts,
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
-                   unsigned long long* clock_probe, const FusedDispatch* dispatch, int fp16) {
+                   unsigned long long* clock_probe, const FusedDispatch* dispatch, int fp16, int64_t avg_rows) {
+  // large batches: CTA pairs halve the token bytes every CTA stages per K step
+  static const int pair_min_rows = [] {
+    const char* e = getenv("MB200_PAIR_MIN_ROWS");
+    return e ? atoi(e) : kPairMinAvgRows;
+  }();
+  const bool pair = pair_min_rows >= 1 && avg_rows >= pair_min_rows && grouped_gemm_pair_capacity(device) >= 32;
   CUtensorMap map_w;
   TokenMaps maps_t;
   GemmArgs g{};
@@ -150,7 +158,7 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
   int rc;
   const int token_cols = mode == kGateUpSwiglu ? hidden : intermediate;
   for (int i = 0; i < kTokenBoxes; ++i)
-    if ((rc = make_tensor_map_2d(&maps_t.m[i], a, 2, uint64_t(cap), uint64_t(token_cols), 16u << i, fp16))) return rc;
+    if ((rc = make_tensor_map_2d(&maps_t.m[i], a, 2, uint64_t(cap), uint64_t(token_cols), (pair ? 8u : 16u) << i, fp16))) return rc;
   if (mode == kGateUpSwiglu) {
     if ((rc = make_tensor_map_2d(&map_w, w, 2, uint64_t(local_experts) * 2 * intermediate, uint64_t(hidden), 128, fp16))) return rc;
     g.n_tiles = (intermediate + 127) / 128;
@@ -167,7 +175,7 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
     g.out_cols = hidden;
   }
   FusedDispatch none{};
-  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, dispatch ? *dispatch : none, device, stream);
+  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, dispatch ? *dispatch : none, device, stream, pair);
 }
 
 int check_shape_fp8(int hidden, int intermediate) {
@@ -290,7 +298,8 @@ int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_cap, const void
   int rc = check_shape(0, hidden, intermediate, local_experts, 1);
   if (rc) return rc;
   return run_gemm_stage(mode, a, row_cap, w, local_experts, hidden, intermediate, counts, mtile_prefix,
-                        sorted_ids, row_scale, out, status, device, as_stream(stream));
+                        sorted_ids, row_scale, out, status, device, as_stream(stream), nullptr, nullptr, 0,
+                        row_cap / local_experts);
 }
 
 int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
@@ -330,6 +339,7 @@ static int moe_forward_16bit(int fp16, const void* hidden_states, const void* w1
   __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(ws + l.act);
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);
 
+  const int64_t avg_rows = tokens * topk / local_experts;  // expected rows per expert picks the kernel variant
   mark_stage(0, s);
   if ((rc = launch_align(topk_ids, tokens * topk, expert_map, local_experts, sched, cap,
                          reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
@@ -349,11 +359,11 @@ static int moe_forward_16bit(int fp16, const void* hidden_states, const void* w1
   mark_stage(2, s);
   if ((rc = run_gemm_stage(kGateUpSwiglu, xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, nullptr, act, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8), &disp, fp16))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 8), &disp, fp16, avg_rows))) return rc;
   mark_stage(3, s);
   if ((rc = run_gemm_stage(kDownWeighted, act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16, avg_rows))) return rc;
   mark_stage(4, s);
   rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s, fp16);
   mark_stage(5, s);

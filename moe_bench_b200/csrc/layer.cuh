@@ -84,9 +84,18 @@ constexpr int kTokenBoxes = 5;
 struct TokenMaps {
   CUtensorMap m[kTokenBoxes];
 };
+// pair: the CTA-pair kernel (cta_group::2); maps_t then holds boxes of 8 << i rows
+// instead of 16 << i.
 int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
                              const GemmArgs& args, const FusedDispatch& dispatch, int device,
-                             cudaStream_t stream);
+                             cudaStream_t stream, bool pair);
+int grouped_gemm_pair_capacity(int device);
+// Rows per expert from which the 16-bit GEMMs run as CTA pairs; 0 = never.  Off by
+// default: in interleaved A/B runs at 8192 tokens the pair kernel, bit-identical in
+// its results, needed the same SM cycles as the single-CTA kernel (both are bound by
+// shared-memory bandwidth: tcgen05.mma operand reads plus the TMA fill), so it buys
+// nothing yet.  The environment variable MB200_PAIR_MIN_ROWS (read once) overrides it.
+constexpr int kPairMinAvgRows = 0;
 
 // grouped_gemm_fp8.cu: e4m3 operands, fp32 block scales applied in the epilogue
 struct GemmFp8Args {
@@ -153,7 +162,7 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
                    unsigned long long* clock_probe = nullptr, const FusedDispatch* dispatch = nullptr,
-                   int fp16 = 0);
+                   int fp16 = 0, int64_t avg_rows = 0);
 int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,
