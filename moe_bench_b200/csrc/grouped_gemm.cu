@@ -50,8 +50,10 @@ constexpr int kThreads = (kFirstDispatchWarp + kDispatchWarps) * 32;
 constexpr int kMaxTokens = 256;
 
 struct SmemTail {
-  // epilogue transposition scratch: per warp two [16 tokens][32 features] 16-bit blocks
-  alignas(16) uint16_t transpose[kEpilogueWarps][2][16 * 32];
+  // epilogue transposition scratch: per warp one [16 tokens][32 features] 16-bit block.
+  // (Every KiB here comes out of the stage ring: at 256-token tiles three 64 KiB stages
+  // must fit, and a build with two stages measured 44 % slower.)
+  alignas(16) uint16_t transpose[kEpilogueWarps + kDispatchWarps][16 * 32];
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
@@ -70,6 +72,7 @@ struct SmemTail {
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr size_t kRingBytes = (kSmemLimit - 1024 - sizeof(SmemTail)) / 1024 * 1024;
 constexpr size_t kSmemBytes = 1024 + kRingBytes + sizeof(SmemTail);
+static_assert(kRingBytes >= 3 * (kWeightBytes + kMaxTokens * 128), "256-token tiles need three stages");
 
 struct Geometry {
   int box_index;    // which token tensor map
@@ -163,6 +166,9 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int E = args.num_experts;
+  // the down GEMM has no dispatch: its warps 10-13 drain accumulators too
+  constexpr int kEpiWarps = kMode == kDownWeighted ? kEpilogueWarps + kDispatchWarps : kEpilogueWarps;
+  constexpr int kChunkStride = kEpiWarps / 4;  // warps per tensor-memory lane quarter
   const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;  // issues the MMAs, owns the full / acc_empty barriers
   const int worker = kPair ? int(blockIdx.x >> 1) : int(blockIdx.x);   // tile stream of this CTA (pair)
@@ -176,9 +182,9 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tail->acc_full[b]), 1);
-      mbar_init(smem_u32(&tail->acc_empty[b]), kEpilogueWarps * (kPair ? 2 : 1));
+      mbar_init(smem_u32(&tail->acc_empty[b]), kEpiWarps * (kPair ? 2 : 1));
     }
-    mbar_init(smem_u32(&tail->epi_bar), kEpilogueWarps);
+    mbar_init(smem_u32(&tail->epi_bar), kEpiWarps);
     tail->abort_flag = 0;
     tail->max_blocks16 = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -411,7 +417,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       args.clock_probe[6 + 3 * kMode] = clock64() - c_start;
     }
 #endif
-  } else if (warp >= kFirstDispatchWarp) {
+  } else if (kMode == kGateUpSwiglu && warp >= kFirstDispatchWarp) {
     // ---------------- fused dispatch (gate/up GEMM): fill the sorted row buffer ----------------
     if (kMode == kGateUpSwiglu && disp.enabled) {
       const int dw = warp - kFirstDispatchWarp;
@@ -447,10 +453,10 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       }
     }
   } else {
-    // ---------------- epilogue: 8 warps, one accumulator row (feature) per thread ----------------
+    // ---------------- epilogue: 8 (gate/up) or 12 (down) warps, one accumulator row (feature) per thread ----------------
     const int ew = warp - kFirstEpilogueWarp;
     const int quarter = warp & 3;     // tensor-memory lanes 32*quarter .. +31
-    const int cgroup = ew >> 2;       // which 16-column chunks this warp takes (even / odd)
+    const int cgroup = ew >> 2;       // which 16-column chunks this warp takes (c mod kChunkStride)
     const int etid = threadIdx.x - kFirstEpilogueWarp * 32;
     uint32_t it = 0;
     uint32_t epi_phase = 0;
@@ -463,7 +469,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       const int par = it & 1;
       if (kMode == kDownWeighted) {
         // per-token destination row and combine weight, shared by all feature rows
-        for (int j = etid; j < tc.ntok; j += kEpilogueWarps * 32) {
+        for (int j = etid; j < tc.ntok; j += kEpiWarps * 32) {
           int a = -1;
           float w = 0.f;
           if (j < tc.valid) {
@@ -488,8 +494,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       // features of a token side by side.  Each 16-token chunk is rounded, transposed
       // through a 1 KiB per-warp block of shared memory and leaves as 16-byte stores
       // (8 features of one token per thread), two per thread and output block.
-      uint16_t* sc0 = tail->transpose[ew][0];
-      uint16_t* sc1 = tail->transpose[ew][1];
+      uint16_t* sc0 = tail->transpose[ew];
       bool released = false;
       auto release = [&]() {
         // every value of this warp's share is in registers: the accumulator may be overwritten
@@ -522,59 +527,59 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
           __syncwarp();
         };
         // two chunks per tensor-memory round trip
-        for (int c = cgroup; c < chunks; c += 4) {
+        for (int c = cgroup; c < chunks; c += 2 * kChunkStride) {
           uint32_t ga[16], ua[16], gb[16], ub[16];
-          const bool two = c + 2 < chunks;
+          const int c2 = c + kChunkStride;
+          const bool two = c2 < chunks;
           tmem_ld16(t0 + c * 16, ga);
           tmem_ld16(t1 + c * 16, ua);
           if (two) {
-            tmem_ld16(t0 + (c + 2) * 16, gb);
-            tmem_ld16(t1 + (c + 2) * 16, ub);
+            tmem_ld16(t0 + c2 * 16, gb);
+            tmem_ld16(t1 + c2 * 16, ub);
           }
           tmem_ld_wait();
-          if (c + 4 >= chunks) release();
+          if (c + 2 * kChunkStride >= chunks) release();
           emit(c, ga, ua);
-          if (two) emit(c + 2, gb, ub);
+          if (two) emit(c2, gb, ub);
         }
       } else {
         const int feat_base = fblock * 256 + quarter * 32;
         auto emit = [&](int c, const uint32_t (&v0)[16], const uint32_t (&v1)[16]) {
           if (c * 16 >= tc.valid) return;
+          // the two 128-row halves of the tile go through the block one after the other
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float w = tail->tile_weight[par][c * 16 + j];
-            sc0[j * 32 + lane] = to_h16(w * __uint_as_float(v0[j]), args.fp16);
-            sc1[j * 32 + lane] = to_h16(w * __uint_as_float(v1[j]), args.fp16);
-          }
-          __syncwarp();
+          for (int half = 0; half < 2; ++half) {
+            const uint32_t (&v)[16] = half == 0 ? v0 : v1;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int piece = lane + 32 * h;
-            const int a = tail->tile_assign[par][c * 16 + (piece >> 2)];
-            const int feat = feat_base + (piece & 3) * 8;
-            if (a >= 0) {
-              uint16_t* dst = out + size_t(a) * args.out_cols + feat;
-              if (feat < args.out_cols)
-                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(sc0 + piece * 8);
-              if (feat + 128 < args.out_cols)
-                *reinterpret_cast<uint4*>(dst + 128) = *reinterpret_cast<const uint4*>(sc1 + piece * 8);
+            for (int j = 0; j < 16; ++j)
+              sc0[j * 32 + lane] = to_h16(tail->tile_weight[par][c * 16 + j] * __uint_as_float(v[j]), args.fp16);
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int piece = lane + 32 * h;
+              const int a = tail->tile_assign[par][c * 16 + (piece >> 2)];
+              const int feat = feat_base + half * 128 + (piece & 3) * 8;
+              if (a >= 0 && feat < args.out_cols)
+                *reinterpret_cast<uint4*>(out + size_t(a) * args.out_cols + feat) =
+                    *reinterpret_cast<const uint4*>(sc0 + piece * 8);
             }
+            __syncwarp();
           }
-          __syncwarp();
         };
-        for (int c = cgroup; c < chunks; c += 4) {
+        for (int c = cgroup; c < chunks; c += 2 * kChunkStride) {
           uint32_t a0[16], a1[16], b0[16], b1[16];
-          const bool two = c + 2 < chunks;
+          const int c2 = c + kChunkStride;
+          const bool two = c2 < chunks;
           tmem_ld16(t0 + c * 16, a0);
           tmem_ld16(t1 + c * 16, a1);
           if (two) {
-            tmem_ld16(t0 + (c + 2) * 16, b0);
-            tmem_ld16(t1 + (c + 2) * 16, b1);
+            tmem_ld16(t0 + c2 * 16, b0);
+            tmem_ld16(t1 + c2 * 16, b1);
           }
           tmem_ld_wait();
-          if (c + 4 >= chunks) release();
+          if (c + 2 * kChunkStride >= chunks) release();
           emit(c, a0, a1);
-          if (two) emit(c + 2, b0, b1);
+          if (two) emit(c2, b0, b1);
         }
       }
       if (!released) release();
