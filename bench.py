@@ -464,8 +464,15 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             roof = {"bound": "tensor", "achieved": gemm_flops / (gemm_ms * 1e-3) / 1e12,
                     "peak": tc_peak, "unit": "TFLOP/s"}
         roof["frac"] = roof["achieved"] / roof["peak"]
+        # DRAM bytes of one gate/up launch from the committed ncu capture of the 32-expert /
+        # 1024-token case (2.075 GB read + 0.151 GB written), scaled by the expert count; only
+        # for workloads with the capture's 32 tokens per expert, where traffic grows in proportion
+        traffic = None
+        if not fp8 and world == 1 and tokens * 32 == EXPERTS * 1024 and args.distribution == "uniform":
+            traffic = 2.226e9 * EXPERTS / 32
         roof.update({
-            "traffic": None, "kernel": f"grouped_gemm_{'fp8' if fp8 else 'bf16'}_kernel<gate_up_swiglu>", "kernel_ms": gemm_ms,
+            "traffic": traffic,
+            "traffic_source": "profiles/grouped_gemm_bf16_E32_T1024_ncu_full.md x experts/32" if traffic else None, "kernel": f"grouped_gemm_{'fp8' if fp8 else 'bf16'}_kernel<gate_up_swiglu>", "kernel_ms": gemm_ms,
             "peak_source": peaks["source"] + " (burst)", "algorithmic_bytes": gemm_bytes,
             "algorithmic_flops": gemm_flops, "t_hbm_ms": t_hbm * 1e3, "t_tensor_ms": t_tc * 1e3,
         })
