@@ -136,12 +136,23 @@ __global__ void reduce_partials_kernel(PeerTable partial, int rank, int world, i
       }
     }
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int p = 0; p < world; ++p) {
-      if (!((owners >> p) & 1u)) continue;
-      const int ring = (rank - p + world) % world;
-      const uint4* src = reinterpret_cast<const uint4*>(partial.ptr[p]) +
-                         (int64_t(ring) * tokens + t) * vec_per_row + v;
-      add_h16x8(*src, acc, fp16);
+    // up to 8 peer loads in flight per thread (an NVLink round trip each), summed in ascending p
+    for (int p0 = 0; p0 < world; p0 += 8) {
+      uint4 val[8];
+      bool have[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int p = p0 + u;
+        have[u] = p < world && ((owners >> p) & 1u);
+        if (have[u]) {
+          const int ring = (rank - p + world) % world;
+          val[u] = *(reinterpret_cast<const uint4*>(partial.ptr[p]) +
+                     (int64_t(ring) * tokens + t) * vec_per_row + v);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (have[u]) add_h16x8(val[u], acc, fp16);
     }
     out[i] = pack_h16x8(acc, fp16);
   }

@@ -25,10 +25,20 @@ __global__ void combine_bf16_kernel(const uint4* __restrict__ y, const int* __re
     const int64_t t = i / vec_per_row;
     const int v = int(i - t * vec_per_row);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int j = 0; j < topk; ++j) {
-      const int64_t n = t * topk + j;
-      if (__ldg(inverse + n) < 0) continue;  // expert on another rank: contributes zero
-      add_h16x8(__ldg(y + n * vec_per_row + v), acc, fp16);
+    // up to 8 row loads in flight per thread, summed in ascending j
+    for (int j0 = 0; j0 < topk; j0 += 8) {
+      uint4 val[8];
+      bool have[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int64_t n = t * topk + j0 + u;
+        // an expert on another rank contributes zero
+        have[u] = j0 + u < topk && __ldg(inverse + n) >= 0;
+        if (have[u]) val[u] = __ldg(y + n * vec_per_row + v);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (have[u]) add_h16x8(val[u], acc, fp16);
     }
     out[i] = pack_h16x8(acc, fp16);
   }
