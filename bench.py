@@ -301,6 +301,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     import torch.distributed as dist
 
     from moe_bench_b200 import capi
+    from moe_bench_b200 import gating as G
     from moe_bench_b200 import problem as P
     from moe_bench_b200.plugin import get_implementation
     from oracle import moe_oracle as O
@@ -320,6 +321,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                                     routing=P.RoutingConfig(distribution=P.Distribution(args.distribution)))
         weights = P.make_weights(cfg)
         x, ids, wts = P._gen_input(cfg, tokens, 0)
+        if args.routing == "logits":
+            # gating front end: router logits -> top-k kernel instead of the generator's direct draw
+            ids, wts = capi.route_topk(G.router_logits(cfg, tokens, 0), TOPK)
         prob = P.MoEProblem(cfg, tokens, x, weights.w1, weights.w2, ids, wts, None, weights.quant_config)
         impl = get_implementation("b200")
         impl.setup(prob)
@@ -333,7 +337,10 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                                     parallel_mode=P.ParallelMode(args.mode), world_size=world, distributed=True,
                                     routing=P.RoutingConfig(distribution=P.Distribution(args.distribution)))
         weights = P.make_weights(cfg, rank)
-        prob = P.make_problem(cfg, tokens, rank, weights=weights)
+        if args.routing == "logits":
+            prob, _ = G.make_routed_problem(cfg, tokens, rank, weights=weights)
+        else:
+            prob = P.make_problem(cfg, tokens, rank, weights=weights)
         x, ids, wts = prob.hidden_states, prob.topk_ids, prob.topk_weights
         impl = get_scheme("b200")
         impl.setup(prob, DistContext(rank=rank, world_size=world, local_rank=local_rank, device=dev))
@@ -472,6 +479,24 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     ms_e2e = timed(e2e_pipelined_step, drain)
 
+    # -------- gating front end as its own stage (not part of the step) --------
+    r_logits = G.router_logits(cfg, tokens, rank)
+    for _ in range(3):
+        capi.route_topk(r_logits, TOPK)
+    rs, re_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rs.record()
+    for _ in range(20):
+        capi.route_topk(r_logits, TOPK)
+    re_.record()
+    torch.cuda.synchronize()
+    route_ms = rs.elapsed_time(re_) / 20
+    route_bytes = r_logits.numel() * 4 + tokens * TOPK * 8
+    front_end = {"kernel": "route_topk_kernel", "ms": route_ms, "bytes": route_bytes,
+                 "achieved_gbs": route_bytes / (route_ms * 1e-3) / 1e9,
+                 "note": "softmax -> top-k -> renormalise over [tokens, experts] fp32 logits; inputs fit L2",
+                 "used_for_step_routing": args.routing == "logits"}
+    del r_logits
+
     # -------- parity spot check (outside any timed region) --------
     out = run().clone()
     idx = torch.randperm(tokens, generator=torch.Generator().manual_seed(0))[: min(8, tokens)].to(dev)
@@ -555,7 +580,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                     "serial_ms_per_step": ms_e2e_serial,
                     "serial_value": flops_step * world / (ms_e2e_serial * 1e-3) / 1e12,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": kernels_per_step * steps,
+            "gpu_launches": kernels_per_step * steps, "front_end": front_end,
             "clocks": dict(clocks.summary(), in_kernel_sm_mhz=kernel_clocks),
             "roofline": roof,
             "stage_ms": dict(zip(stage_names, stage_ms)),
@@ -608,6 +633,9 @@ def main() -> None:
                          "fp16 = the bf16 kernels with IEEE-half tensors")
     ap.add_argument("--mode", default="ep", choices=["ep", "tp"], help="parallel mode when --gpus > 1")
     ap.add_argument("--distribution", default="uniform", choices=["uniform", "single", "skewed", "balanced"])
+    ap.add_argument("--routing", default="data", choices=["data", "logits"],
+                    help="data = topk_ids/topk_weights drawn as the reference's generator does (the headline); "
+                         "logits = router logits through the library's top-k kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true", help="skip the vLLM fused_experts baseline leg")
     ap.add_argument("--experts", type=int, default=256, help="expert count (lower it only to size a profiler capture)")
