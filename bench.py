@@ -558,6 +558,21 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "peak_source": peaks["source"] + " (burst)", "algorithmic_bytes": gemm_bytes,
             "algorithmic_flops": gemm_flops, "t_hbm_ms": t_hbm * 1e3, "t_tensor_ms": t_tc * 1e3,
         })
+        # the other stages against the same peaks (single GPU; the multi-GPU stages contain barriers)
+        stage_roofline = None
+        if world == 1:
+            def _entry(ms, nbytes, flops):
+                t_b, t_f = nbytes / (peaks["hbm_gbs"] * 1e9), flops / (tc_peak * 1e12)
+                return {"ms": ms, "algorithmic_bytes": nbytes, "algorithmic_flops": flops,
+                        "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "achieved_tflops": flops / (ms * 1e-3) / 1e12,
+                        "bound": "hbm" if t_b >= t_f else "tensor", "frac": max(t_b, t_f) / (ms * 1e-3)}
+            down_bytes = touched * n_local * HIDDEN * wb + rows * n_local * wb + rows * HIDDEN * 2
+            stage_roofline = {
+                "align": _entry(stage_ms[0], assignments * 12, 0.0),
+                "gate_up_gemm": _entry(stage_ms[2], gemm_bytes, gemm_flops),
+                "down_gemm": _entry(stage_ms[3], down_bytes, 2.0 * INTER * HIDDEN * assignments),
+                "combine": _entry(stage_ms[4], (assignments + tokens) * HIDDEN * 2, 0.0),
+            }
         layer_bytes = touched * 3 * n_local * HIDDEN * wb + 2 * tokens * HIDDEN * 2 + assignments * 8
         layer_roof_ms = max(layer_bytes / (peaks["hbm_gbs"] * 1e9), flops_step / (tc_peak * 1e12)) * 1e3
         # kernels of this library launched per step (memsets and copies are not kernels)
@@ -584,7 +599,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "clocks": dict(clocks.summary(), in_kernel_sm_mhz=kernel_clocks),
             "roofline": roof,
             "stage_ms": dict(zip(stage_names, stage_ms)),
-            "stage_ms_by_rank": stage_by_rank,
+            "stage_ms_by_rank": stage_by_rank, "stage_roofline": stage_roofline,
             "layer_roofline_ms": layer_roof_ms, "layer_roofline_frac": layer_roof_ms / ms_step,
             "latency_us": ms_step * 1e3,
             "verify": "ok" if passed else "FAIL", "rel_err": check.rel_err,
