@@ -61,6 +61,7 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.errors, self.power_w, self._index = set(), 0.0, index
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -77,17 +78,51 @@ class ClockSampler:
         0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
     }
 
+    def _reason_bits(self):
+        """Current clock-event (throttle) reason bitmask; NVML renamed the call, so try both."""
+        nv = self._nv
+        for fn in ("nvmlDeviceGetCurrentClocksEventReasons", "nvmlDeviceGetCurrentClocksThrottleReasons"):
+            if hasattr(nv, fn):
+                try:
+                    return int(getattr(nv, fn)(self._h))
+                except Exception as exc:  # noqa: BLE001
+                    self.errors.add(f"{fn}: {exc}")
+        return None
+
+    def _reasons_from_smi(self):
+        """Fallback when NVML does not answer: the same flags through nvidia-smi (read-only query)."""
+        import subprocess
+
+        fields = ["sw_power_cap", "hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"]
+        try:
+            out = subprocess.run(
+                ["nvidia-smi", "-i", str(self._index), "--format=csv,noheader",
+                 "--query-gpu=" + ",".join("clocks_event_reasons." + f for f in fields)],
+                capture_output=True, text=True, timeout=5).stdout.strip().split(",")
+            for name, val in zip(fields, out):
+                if val.strip().lower() == "active":
+                    self.reasons.add(name)
+        except Exception as exc:  # noqa: BLE001
+            self.errors.add(f"nvidia-smi: {exc}")
+
     def _loop(self):
         nv = self._nv
+        n = 0
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
-                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                self.power_w = max(self.power_w, nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+            except Exception as exc:  # noqa: BLE001
+                self.errors.add(f"clock/power: {exc}")
+            bits = self._reason_bits()
+            if bits is None:
+                if n % 20 == 0:
+                    self._reasons_from_smi()
+            else:
                 for bit, name in self._NAMES.items():
                     if bits & bit:
                         self.reasons.add(name)
-            except Exception:  # noqa: BLE001
-                pass
+            n += 1
             time.sleep(0.01)
 
     def __enter__(self):
@@ -105,8 +140,11 @@ class ClockSampler:
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
         s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(s)}
+        out = {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+               "samples": len(s), "power_w_max": round(self.power_w, 1)}
+        if self.errors:
+            out["sampler_errors"] = sorted(self.errors)[:3]
+        return out
 
 
 def _touched_experts(topk_ids) -> int:

@@ -122,3 +122,44 @@ def test_scheme_world2(mode, precision, tokens, dist_name):
         assert status == 0, f"rank {rank}: device status {status} ({msg})"
         assert same, f"rank {rank}: repeated runs differ"
         assert passed and rel < 3e-2, f"rank {rank} [{backend}]: {msg} rel={rel}"
+
+
+def test_barrier_with_absent_peer_gives_up_with_a_status_and_the_context_stays_usable():
+    """Failure detection without a fault: two local buffers stand in for the flag
+    areas of two ranks and only rank 0 calls the barrier, so the flag it polls is
+    never set.  The kernel gives up after its 3 s limit, reports 150 + the missing
+    peer in the status word and returns; the late "rank" then completes the same
+    barrier at once, and the layer still runs in this context."""
+    import time
+
+    from moe_bench_b200 import capi
+    from moe_bench_b200.plugin import get_implementation
+
+    dev = torch.device("cuda", 0)
+    bufs = [torch.zeros(1024, dtype=torch.int32, device=dev) for _ in range(2)]
+    ptrs = capi.peer_pointer_array([b.data_ptr() for b in bufs])
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    capi.peer_barrier(ptrs, 0, 2, 1, status, dev)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 2.5 < waited < 20, waited
+    assert int(status.item()) == 151           # 100 (a wait ran out) + 50 (barrier) + peer 1
+    assert int(bufs[0][0]) == 1 and int(bufs[1][0]) == 1   # rank 0 had announced itself to both
+    # the missing rank arrives late: its barrier and a repeat of rank 0's complete immediately
+    status.zero_()
+    t0 = time.time()
+    capi.peer_barrier(ptrs, 1, 2, 1, status, dev)
+    capi.peer_barrier(ptrs, 0, 2, 1, status, dev)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0 and int(status.item()) == 0
+    # the context is intact
+    cfg = _cfg("ep", "bf16", 1)
+    prob = _to_dev(P.make_problem(cfg, 50, 0), "cuda:0")
+    impl = get_implementation("b200")
+    impl.setup(prob)
+    out = impl.run(prob)
+    assert impl.device_status() == 0
+    res = O.verify_output("bf16", out, O.reference_moe(prob))
+    assert res.passed, res.message
