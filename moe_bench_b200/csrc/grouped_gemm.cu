@@ -5,8 +5,11 @@
 // 16 up to 256).  Expert segments are therefore padded to 16 rows only, a tile
 // takes as many tokens as the expert has (up to 256), and a 64-deep K step moves
 // 32 KB of weights + at most 32 KB of tokens into shared memory for two
-// 128 x ntok x 64 products - half the bytes per MMA cycle of a 128-token tile,
-// which is what bounds the kernel (shared-memory fill from L2).
+// 128 x ntok x 64 products - half the bytes per MMA cycle of a 128-token tile.
+// A 128 x N x 16 tcgen05.mma takes N/2 cycles, but a K step of a tile costs about
+// 1000 cycles whatever its N between 16 and 224 (the stage pipeline, not the
+// tensor pipe, paces it), so the fewest, fullest tiles win: segments longer than
+// 256 rows are split into equal parts.
 //
 //   gate/up:  acc0 = w1[e, f0:f0+128, :] . X^T, acc1 = w1[e, N+f0 : N+f0+128, :] . X^T
 //             act[token, f0+i] = SiLU(acc0[i, token]) * acc1[i, token]      (bf16)
@@ -17,19 +20,26 @@
 // kernels/tileoverlap/common/sm120_common.cuh:149-274).
 //
 // One persistent CTA per SM, 448 threads: warp 0 issues TMA loads into a ring of
-// 128-byte-swizzled stages, warp 1 owns tensor memory and issues tcgen05.mma,
-// warps 2-9 drain the accumulators (tcgen05.ld) and write the output, warps
-// 10-13 are the fused dispatch of the gate/up GEMM: they copy token rows (local,
-// or P2P loads from the source ranks over NVLink) into the sorted row buffer one
-// 16-row granule at a time, granules strided over the CTAs in row order, and
-// count each granule's arrival; the TMA warp starts a tile only when all
-// granules of its token block have arrived (acquire on the counters, then a
-// proxy fence).  Dispatch warps never wait, so a cooperative launch (all CTAs
-// resident) makes the scheme deadlock-free.  The token
-// box (16/32/64/128/256 rows), the stage size, the number of stages and whether
-// the accumulators are double-buffered (token box <= 128) are derived on the
-// device from the largest expert segment in the schedule, so one launch suits a
-// 1-token and an 8192-token batch.  Every wait is bounded.
+// 128-byte-swizzled stages (32 KiB of weights + exactly the tile's token rows, one
+// TMA box per set bit of ntok/16), warp 1 owns tensor memory and issues tcgen05.mma,
+// warps 2-9 drain the accumulators: tcgen05.ld of two 16-token chunks per round
+// trip, accumulator released after the warp's last load, each chunk rounded,
+// transposed through a 1 KiB per-warp block of shared memory and stored as 16-byte
+// vectors (8 features of one token per thread).  Warps 10-13 are the fused dispatch
+// of the gate/up GEMM: they copy token rows (local, or P2P loads from the source
+// ranks over NVLink) into the sorted row buffer one 16-row granule at a time,
+// granules strided over the CTAs in row order, and count each granule's arrival;
+// the TMA warp starts a tile only when all granules of its token block have
+// arrived (acquire on the counters, then a proxy fence).  Dispatch warps never
+// wait, so a cooperative launch (all CTAs resident) makes the scheme deadlock-free.
+// In the down GEMM, which has no dispatch, warps 10-13 drain accumulators too.
+// The token box (16/32/64/128/256 rows), the stage size, the number of stages and
+// whether the accumulators are double-buffered (token box <= 128) are derived on
+// the device from the largest expert segment in the schedule, so one launch suits
+// a 1-token and an 8192-token batch.  Every wait is bounded.
+//
+// kPair (opt-in) runs every tile on a cluster of two CTAs with
+// tcgen05.mma.cta_group::2; see the kernel's comment.
 
 #include "layer.cuh"
 
