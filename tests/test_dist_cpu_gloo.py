@@ -37,7 +37,7 @@ def _worker(rank, world, port, mode, precision, out_q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,precision", [("ep", "bf16"), ("tp", "bf16"), ("ep", "fp8"), ("tp", "fp8")])
+@pytest.mark.parametrize("mode,precision", [("ep", "bf16"), ("tp", "bf16"), ("ep", "fp8"), ("tp", "fp8"), ("ep", "fp16"), ("tp", "fp16")])
 def test_distributed_dataflow_model_world2(mode, precision):
     world = 2
     port = 29500 + (os.getpid() + hash((mode, precision))) % 2000
