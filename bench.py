@@ -552,6 +552,40 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     gpu_base = {"unavailable": "skipped (--no-gpu-baseline)"}
     if not args.no_gpu_baseline:
         gpu_base = _time_vllm_baseline(prob, world, dev, flops_step, barrier, max_over_ranks, out)
+    # -------- decomposition: the rank's GEMM work with every token already local --------
+    decomposition = None
+    if args.decompose and world > 1:
+        full_x = torch.empty(world * tokens, HIDDEN, dtype=x.dtype, device=dev)
+        full_ids = torch.empty(world * tokens, TOPK, dtype=ids.dtype, device=dev)
+        full_w = torch.empty(world * tokens, TOPK, dtype=wts.dtype, device=dev)
+        dist.all_gather_into_tensor(full_x, x.contiguous())
+        dist.all_gather_into_tensor(full_ids, ids.contiguous())
+        dist.all_gather_into_tensor(full_w, wts.contiguous())
+        ep = args.mode == "ep"
+        comp_prob = P.MoEProblem(cfg, world * tokens, full_x, prob.w1, prob.w2, full_ids, full_w,
+                                 prob.expert_map if ep else None, prob.quant_config)
+        comp = get_implementation("b200")
+        comp.setup(comp_prob)
+        for _ in range(max(3, warmup)):
+            comp.run(comp_prob)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(steps):
+            comp.run(comp_prob)
+        c1.record()
+        torch.cuda.synchronize()
+        barrier()
+        ms_comp = max_over_ranks(c0.elapsed_time(c1) / steps)
+        decomposition = {
+            "t_fused_ms": ms_step, "t_comp_alone_ms": ms_comp, "t_comm_exposed_ms": ms_step - ms_comp,
+            "comm_stage_ms_in_fused": stage_ms[0] + stage_ms[1] + stage_ms[4],
+            "note": "comp alone = the single-GPU forward of this rank's experts (EP) or weight shard (TP) over "
+                    "all W*T tokens gathered beforehand; exposed communication = fused - comp alone; the stage "
+                    "sum is routing exchange + dispatch + combine/reduce incl. their barriers in the fused run",
+        }
+        del comp, comp_prob, full_x, full_ids, full_w
+
     if world > 1:
         ok = torch.tensor([1.0 if check.passed else 0.0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
@@ -633,7 +667,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
                     "serial_ms_per_step": ms_e2e_serial,
                     "serial_value": flops_step * world / (ms_e2e_serial * 1e-3) / 1e12,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": kernels_per_step * steps, "front_end": front_end,
+            "gpu_launches": kernels_per_step * steps, "front_end": front_end, "decomposition": decomposition,
             "clocks": dict(clocks.summary(), in_kernel_sm_mhz=kernel_clocks),
             "roofline": roof,
             "stage_ms": dict(zip(stage_names, stage_ms)),
@@ -689,6 +723,8 @@ def main() -> None:
     ap.add_argument("--routing", default="data", choices=["data", "logits"],
                     help="data = topk_ids/topk_weights drawn as the reference's generator does (the headline); "
                          "logits = router logits through the library's top-k kernel")
+    ap.add_argument("--decompose", action="store_true",
+                    help="N > 1: also time the rank's computation alone (all tokens local) next to the fused step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true", help="skip the vLLM fused_experts baseline leg")
     ap.add_argument("--experts", type=int, default=256, help="expert count (lower it only to size a profiler capture)")
