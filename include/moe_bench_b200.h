@@ -132,7 +132,11 @@ int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int int
  * hidden_states [tokens, hidden] bf16; w1 [E_local, 2*intermediate, hidden]
  * (gate rows, then up rows); w2 [E_local, hidden, intermediate]; out
  * [tokens, hidden] bf16.  The workspace may be reused by the next call on the
- * same stream; calls that overlap on the device need separate workspaces. */
+ * same stream; calls that overlap on the device need separate workspaces.
+ * Environment (read once per process, at the first 16-bit GEMM launch):
+ * MB200_PAIR_MIN_ROWS=<n> runs the grouped GEMMs as CTA pairs
+ * (tcgen05.mma.cta_group::2) when tokens*topk/local_experts >= n; results are
+ * bit-identical; unset or < 1 = single-CTA kernels. */
 int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void* w2,
                            const int32_t* topk_ids, const float* topk_weights,
                            const int32_t* expert_map, void* out, int64_t tokens, int hidden,
