@@ -42,21 +42,29 @@ def _inputs() -> list:
 
 
 def needs_build() -> bool:
-    if not os.path.exists(LIB_PATH):
-        return True
-    built = os.path.getmtime(LIB_PATH)
-    return any(os.path.getmtime(f) > built for f in _inputs())
+    return not _up_to_date(LIB_PATH)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
-        return LIB_PATH
+def _up_to_date(path: str) -> bool:
+    if not os.path.exists(path):
+        return False
+    built = os.path.getmtime(path)
+    return not any(os.path.getmtime(f) > built for f in _inputs())
+
+
+def build(force: bool = False, verbose: bool = False, variant: str = "", defines=()) -> str:
+    """Build the library.  ``variant`` / ``defines`` build a differently named copy with
+    extra ``-D`` flags (``libmoe_bench_b200_<variant>.so``), used by the diagnostics."""
+    lib_path = LIB_PATH if not variant else os.path.join(PKG, f"libmoe_bench_b200_{variant}.so")
+    obj_dir = OBJ_DIR if not variant else os.path.join(PKG, "build", variant)
+    if not force and _up_to_date(lib_path):
+        return lib_path
     nvcc = _nvcc()
-    os.makedirs(OBJ_DIR, exist_ok=True)
-    extra = ["-Xptxas", "-v"] if verbose else []
+    os.makedirs(obj_dir, exist_ok=True)
+    extra = (["-Xptxas", "-v"] if verbose else []) + [f"-D{d}" for d in defines]
 
     def compile_one(src: str) -> str:
-        obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
+        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or res.returncode:
@@ -67,17 +75,39 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
         objs = list(pool.map(compile_one, SOURCES))
-    link = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    link = [nvcc, "-shared", "-o", lib_path, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode:
         sys.stderr.write(res.stdout + res.stderr)
         raise RuntimeError("link failed")
-    return LIB_PATH
+    return lib_path
+
+
+PROBE_VARIANT = ("probe", ("MB200_PROBE_WAITS",))
+MMA_RATE_SRC = os.path.join(CSRC, "diag_mma_rate.cu")
+MMA_RATE_BIN = os.path.join(PKG, "diag_mma_rate")
+
+
+def build_diagnostics(force: bool = False) -> tuple:
+    """The diagnostics' two artefacts: the library with the MMA warp's wait counters
+    compiled in, and the stand-alone tcgen05.mma issue-rate microbenchmark."""
+    probe = build(force=force, variant=PROBE_VARIANT[0], defines=PROBE_VARIANT[1])
+    if force or not _up_to_date(MMA_RATE_BIN):
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+               "-o", MMA_RATE_BIN, MMA_RATE_SRC]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError("nvcc failed on diag_mma_rate.cu")
+    return probe, MMA_RATE_BIN
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--diagnostics", action="store_true", help="also build the diagnostics' probe library and tool")
     a = ap.parse_args()
     print(build(force=a.force, verbose=a.verbose))
+    if a.diagnostics:
+        print(*build_diagnostics(force=a.force), sep="\n")

@@ -87,26 +87,38 @@ class MB200Error(RuntimeError):
 _lib: Optional[ctypes.CDLL] = None
 
 
+def load_library(path: str) -> ctypes.CDLL:
+    """Open a build of the library, set the prototypes and check its ABI version."""
+    if not os.path.exists(path):
+        raise MB200Error(
+            f"{path} is missing: build it with `python -m moe_bench_b200.build` "
+            "(there is no non-CUDA fallback)"
+        )
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    if lib.mb200_abi_version() != ABI_VERSION:
+        raise MB200Error(
+            f"{path} has ABI version {lib.mb200_abi_version()}, this package needs {ABI_VERSION}: "
+            "rebuild with `python -m moe_bench_b200.build --force`"
+        )
+    return lib
+
+
 def load() -> ctypes.CDLL:
     """Load the shared library (once) and set the prototypes."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            raise MB200Error(
-                f"{LIB_PATH} is missing: build it with `python -m moe_bench_b200.build` "
-                "(there is no non-CUDA fallback)"
-            )
-        lib = ctypes.CDLL(LIB_PATH)
-        for name, (res, args) in SIGNATURES.items():
-            fn = getattr(lib, name)
-            fn.restype, fn.argtypes = res, args
-        if lib.mb200_abi_version() != ABI_VERSION:
-            raise MB200Error(
-                f"{LIB_PATH} has ABI version {lib.mb200_abi_version()}, this package needs {ABI_VERSION}: "
-                "rebuild with `python -m moe_bench_b200.build --force`"
-            )
-        _lib = lib
+        _lib = load_library(LIB_PATH)
     return _lib
+
+
+def use_library(lib: ctypes.CDLL) -> None:
+    """Route every later call of this module to ``lib`` (a result of ``load_library``);
+    the diagnostics use it to compare two builds in one process."""
+    global _lib
+    _lib = lib
 
 
 def _check(rc: int, what: str) -> None:
