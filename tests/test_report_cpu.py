@@ -1,0 +1,33 @@
+"""The report module on a measured ``bench.py`` line kept as a fixture."""
+
+import json
+import os
+
+from moe_bench_b200 import report as R
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SAMPLE = os.path.join(HERE, "golden", "bench_line_sample.json")
+
+
+def test_reference_row_keys_and_extensions():
+    line = json.load(open(SAMPLE))
+    row = R.rows_from_bench(line)
+    # the reference's columns (report.py:13-23)
+    for key in ("num_tokens", "latency_us", "tflops", "local_assignments", "timing", "rel_err", "verify"):
+        assert key in row
+    assert row["num_tokens"] == 8192 and row["local_assignments"] == 8192 * 8
+    assert abs(row["latency_us"] - line["ms_per_step"] * 1e3) < 1e-9
+    # 6*N*K flop per assignment (reference bench.py:40-49)
+    assert abs(row["tflops"] - 6 * 2048 * 7168 * 65536 / (row["latency_us"] * 1e-6) / 1e12) < 1e-6 * row["tflops"]
+    assert 0 < row["roofline_frac"] <= 1.2 and row["vllm_us"] > row["latency_us"]
+    assert set(row["stage_achieved"]) == {"align", "gate_up_gemm", "down_gemm", "combine"}
+    pay = R.payload([row], line["config"])
+    assert set(pay) == {"config", "implementation", "results"}      # report.py:68-81
+
+
+def test_table_renders(tmp_path, capsys):
+    out = tmp_path / "rows.json"
+    R.main([SAMPLE, "--json", str(out)])
+    text = capsys.readouterr().out
+    assert "TFLOP/s" in text and "gate_up_gemm" in text and "8192" in text
+    assert json.load(open(out))["results"][0]["verify"] == "ok"
