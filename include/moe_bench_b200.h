@@ -114,13 +114,29 @@ int mb200_group_quant_fp8(const void* x, int64_t rows, int hidden, void* q, floa
  * the sorted rows, w1 [E, 2N, hidden], act [row_capacity, N] (reference.py:113-114).
  * mode 1: y[n, 0:hidden] = row_scale[n] * (a.w2[e]) for a [row_capacity, N],
  * w2 [E, hidden, N], y [tokens*topk, hidden] indexed by the flat assignment n
- * (reference.py:115,180-181).  status: one int32 in device memory, zeroed by
- * the caller. */
+ * (reference.py:115,180-181).  status: the head of a status block in device
+ * memory, two int32 zeroed by the caller: [0] receives the first failure code of
+ * a kernel (0 = none), [1] is the limit of one in-kernel wait in milliseconds
+ * (0 = the default of 4 s). */
 int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_capacity, const void* w,
                             int local_experts, int hidden, int intermediate, const int32_t* counts,
                             const int32_t* mtile_prefix, const int32_t* sorted_ids,
                             const float* row_scale, void* out, int32_t* status, int device,
                             void* stream);
+
+/* The gate/up stage (mode 0 above) for rows that SOMEONE ELSE delivers while the
+ * kernel runs: another kernel on another stream, or a peer GPU that pushes rows
+ * into `a` (the reference's push dispatch signals row blocks the same way,
+ * kernels/tk/tk_moe.cu:647-821).  granule_done[row_capacity/16] counts arrivals
+ * per 16-row granule of `a`; the kernel loads a token block only after every
+ * granule it spans has reached granule_target (acquire), and gives up with
+ * status 106 when one does not within the wait limit of the status block -
+ * the launch then ends normally and the context stays usable. */
+int mb200_grouped_gemm_bf16_gated(const void* a, int64_t row_capacity, const void* w, int local_experts,
+                                  int hidden, int intermediate, const int32_t* counts,
+                                  const int32_t* mtile_prefix, const int32_t* sorted_ids,
+                                  const int32_t* granule_done, int granule_target, void* out,
+                                  int32_t* status, int device, void* stream);
 
 /* Bytes of caller-provided workspace for one forward of the given shape. */
 int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
@@ -133,10 +149,13 @@ int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int int
  * (gate rows, then up rows); w2 [E_local, hidden, intermediate]; out
  * [tokens, hidden] bf16.  The workspace may be reused by the next call on the
  * same stream; calls that overlap on the device need separate workspaces.
- * Environment (read once per process, at the first 16-bit GEMM launch):
- * MB200_PAIR_MIN_ROWS=<n> runs the grouped GEMMs as CTA pairs
- * (tcgen05.mma.cta_group::2) when tokens*topk/local_experts >= n; results are
- * bit-identical; unset or < 1 = single-CTA kernels. */
+ * The first 256 bytes of the workspace are the status block: the caller zeroes
+ * them once before the first call (and again after a reported failure).  Word 0
+ * keeps the FIRST failure code of any kernel (100 + site: a bounded in-kernel
+ * wait ran out; 150 + peer: a cross-GPU barrier did); while it is non-zero the
+ * outputs are not to be trusted - read it with mb200_read_status at a point
+ * where the host synchronises anyway.  Word 1 is the limit of one in-kernel
+ * wait in milliseconds (0 = 4 s). */
 int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void* w2,
                            const int32_t* topk_ids, const float* topk_weights,
                            const int32_t* expert_map, void* out, int64_t tokens, int hidden,

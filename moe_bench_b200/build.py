@@ -54,7 +54,7 @@ def _up_to_date(path: str) -> bool:
 
 def build(force: bool = False, verbose: bool = False, variant: str = "", defines=()) -> str:
     """Build the library.  ``variant`` / ``defines`` build a differently named copy with
-    extra ``-D`` flags (``libmoe_bench_b200_<variant>.so``), used by the diagnostics."""
+    extra ``-D`` flags (``libmoe_bench_b200_<variant>.so``), for comparing two builds side by side."""
     lib_path = LIB_PATH if not variant else os.path.join(PKG, f"libmoe_bench_b200_{variant}.so")
     obj_dir = OBJ_DIR if not variant else os.path.join(PKG, "build", variant)
     if not force and _up_to_date(lib_path):
@@ -83,31 +83,9 @@ def build(force: bool = False, verbose: bool = False, variant: str = "", defines
     return lib_path
 
 
-PROBE_VARIANT = ("probe", ("MB200_PROBE_WAITS",))
-MMA_RATE_SRC = os.path.join(CSRC, "diag_mma_rate.cu")
-MMA_RATE_BIN = os.path.join(PKG, "diag_mma_rate")
-
-
-def build_diagnostics(force: bool = False) -> tuple:
-    """The diagnostics' two artefacts: the library with the MMA warp's wait counters
-    compiled in, and the stand-alone tcgen05.mma issue-rate microbenchmark."""
-    probe = build(force=force, variant=PROBE_VARIANT[0], defines=PROBE_VARIANT[1])
-    if force or not _up_to_date(MMA_RATE_BIN):
-        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
-               "-o", MMA_RATE_BIN, MMA_RATE_SRC]
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode:
-            sys.stderr.write(res.stdout + res.stderr)
-            raise RuntimeError("nvcc failed on diag_mma_rate.cu")
-    return probe, MMA_RATE_BIN
-
-
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
-    ap.add_argument("--diagnostics", action="store_true", help="also build the diagnostics' probe library and tool")
     a = ap.parse_args()
     print(build(force=a.force, verbose=a.verbose))
-    if a.diagnostics:
-        print(*build_diagnostics(force=a.force), sep="\n")

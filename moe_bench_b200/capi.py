@@ -39,6 +39,10 @@ SIGNATURES = {
         c_i32,
         [c_i32, c_vp, c_i64, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp],
     ),
+    "mb200_grouped_gemm_bf16_gated": (
+        c_i32,
+        [c_vp, c_i64, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_vp],
+    ),
     "mb200_workspace_bytes": (c_i64, [c_i32, c_i64, c_i32, c_i32, c_i32, c_i32]),
     "mb200_moe_forward_bf16": (
         c_i32,
@@ -116,7 +120,7 @@ def load() -> ctypes.CDLL:
 
 def use_library(lib: ctypes.CDLL) -> None:
     """Route every later call of this module to ``lib`` (a result of ``load_library``);
-    the diagnostics use it to compare two builds in one process."""
+    lets one process compare two builds."""
     global _lib
     _lib = lib
 
@@ -239,6 +243,25 @@ def grouped_gemm_bf16(mode, a, w, hidden, intermediate, counts, prefix, sorted_i
             _ptr(prefix), _ptr(sorted_ids), _ptr(row_scale), _ptr(out), _ptr(status), dev.index or 0, _stream(dev),
         ),
         "grouped_gemm_bf16",
+    )
+
+
+def grouped_gemm_bf16_gated(a, w, hidden, intermediate, counts, prefix, sorted_ids, granule_done, granule_target,
+                            out, status):
+    """The gate/up stage for rows delivered by someone else: a token block is loaded once
+    ``granule_done`` of each of its 16-row granules has reached ``granule_target``."""
+    dev = a.device
+    _need(granule_done, torch.int32, "granule_done")
+    _need(status, torch.int32, "status")
+    if status.numel() < 2:
+        raise MB200Error("status: need the two-word head of a status block")
+    _check(
+        load().mb200_grouped_gemm_bf16_gated(
+            _ptr(a), a.shape[0], _ptr(w), w.shape[0], hidden, intermediate, _ptr(counts), _ptr(prefix),
+            _ptr(sorted_ids), _ptr(granule_done), granule_target, _ptr(out), _ptr(status), dev.index or 0,
+            _stream(dev),
+        ),
+        "grouped_gemm_bf16_gated",
     )
 
 

@@ -1,6 +1,7 @@
 // extern "C" entry points (declared in include/moe_bench_b200.h), tensor-map
 // creation and the workspace layout of the forward.
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -23,6 +24,21 @@ void mark_stage(int i, cudaStream_t s) {
   if (i < g_stage_event_count && g_stage_events[i]) cudaEventRecord(g_stage_events[i], s);
 }
 
+int device_sm_count(int device) {
+  static std::atomic<int> cached[kMaxDevices];
+  if (device >= 0 && device < kMaxDevices) {
+    const int v = cached[device].load(std::memory_order_relaxed);
+    if (v > 0) return v;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (device >= 0 && device < kMaxDevices) cached[device].store(sms, std::memory_order_relaxed);
+  return sms;
+}
+
 void set_last_error(const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -41,14 +57,15 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
+  // initialised once, thread-safe (C++11 static initialisation)
+  static const EncodeTiledFn fn = [] {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
+      return reinterpret_cast<EncodeTiledFn>(p);
+    return EncodeTiledFn(nullptr);
+  }();
   return fn;
 }
 }  // namespace
@@ -113,9 +130,13 @@ Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, 
   l.xs = l.acts = 0;
   l.granule_bytes = precision == MB200_PRECISION_FP8 ? 0 : (cap / kPadBf16 + 1) * 4;
   l.granules = take(l.granule_bytes);
+  l.xq_tok = l.xs_tok = 0;
   if (precision == MB200_PRECISION_FP8) {
     l.xs = take(int64_t(hidden / 128) * cap * 4);
     l.acts = take(int64_t(intermediate / 128) * cap * 4);
+    // every token quantised once; the sorted rows are gathered from here
+    l.xq_tok = take(tokens * hidden);
+    l.xs_tok = take(tokens * int64_t(hidden / 128) * 4);
   }
   l.total = off;
   return l;
@@ -136,13 +157,7 @@ int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts,
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
-                   unsigned long long* clock_probe, const FusedDispatch* dispatch, int fp16, int64_t avg_rows) {
-  // large batches: CTA pairs halve the token bytes every CTA stages per K step
-  static const int pair_min_rows = [] {
-    const char* e = getenv("MB200_PAIR_MIN_ROWS");
-    return e ? atoi(e) : kPairMinAvgRows;
-  }();
-  const bool pair = pair_min_rows >= 1 && avg_rows >= pair_min_rows && grouped_gemm_pair_capacity(device) >= 32;
+                   unsigned long long* clock_probe, const FusedDispatch* dispatch, int fp16) {
   CUtensorMap map_w;
   TokenMaps maps_t;
   GemmArgs g{};
@@ -158,7 +173,7 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
   int rc;
   const int token_cols = mode == kGateUpSwiglu ? hidden : intermediate;
   for (int i = 0; i < kTokenBoxes; ++i)
-    if ((rc = make_tensor_map_2d(&maps_t.m[i], a, 2, uint64_t(cap), uint64_t(token_cols), (pair ? 8u : 16u) << i, fp16))) return rc;
+    if ((rc = make_tensor_map_2d(&maps_t.m[i], a, 2, uint64_t(cap), uint64_t(token_cols), 16u << i, fp16))) return rc;
   if (mode == kGateUpSwiglu) {
     if ((rc = make_tensor_map_2d(&map_w, w, 2, uint64_t(local_experts) * 2 * intermediate, uint64_t(hidden), 128, fp16))) return rc;
     g.n_tiles = (intermediate + 127) / 128;
@@ -175,7 +190,7 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
     g.out_cols = hidden;
   }
   FusedDispatch none{};
-  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, dispatch ? *dispatch : none, device, stream, pair);
+  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, dispatch ? *dispatch : none, device, stream);
 }
 
 int check_shape_fp8(int hidden, int intermediate) {
@@ -298,8 +313,26 @@ int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_cap, const void
   int rc = check_shape(0, hidden, intermediate, local_experts, 1);
   if (rc) return rc;
   return run_gemm_stage(mode, a, row_cap, w, local_experts, hidden, intermediate, counts, mtile_prefix,
-                        sorted_ids, row_scale, out, status, device, as_stream(stream), nullptr, nullptr, 0,
-                        row_cap / local_experts);
+                        sorted_ids, row_scale, out, status, device, as_stream(stream), nullptr, nullptr, 0);
+}
+
+int mb200_grouped_gemm_bf16_gated(const void* a, int64_t row_cap, const void* w, int local_experts, int hidden,
+                                  int intermediate, const int32_t* counts, const int32_t* mtile_prefix,
+                                  const int32_t* sorted_ids, const int32_t* granule_done, int granule_target,
+                                  void* out, int32_t* status, int device, void* stream) {
+  MB200_REQUIRE(a && w && counts && mtile_prefix && sorted_ids && out && granule_done && status, kInvalidArgument,
+                "grouped_gemm_gated: null pointer");
+  MB200_REQUIRE(granule_target >= 1, kInvalidArgument, "grouped_gemm_gated: granule_target=%d", granule_target);
+  MB200_REQUIRE(row_cap > 0 && row_cap % kPadBf16 == 0, kInvalidArgument,
+                "grouped_gemm_gated: row capacity %lld must be a positive multiple of %d", (long long)row_cap, kPadBf16);
+  int rc = check_shape(0, hidden, intermediate, local_experts, 1);
+  if (rc) return rc;
+  FusedDispatch gate{};
+  gate.granule_done = const_cast<int*>(granule_done);
+  gate.granule_target = granule_target;
+  gate.enabled = kDispatchExternal;
+  return run_gemm_stage(kGateUpSwiglu, a, row_cap, w, local_experts, hidden, intermediate, counts, mtile_prefix,
+                        sorted_ids, nullptr, out, status, device, as_stream(stream), nullptr, &gate, 0);
 }
 
 int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
@@ -339,7 +372,6 @@ static int moe_forward_16bit(int fp16, const void* hidden_states, const void* w1
   __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(ws + l.act);
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);
 
-  const int64_t avg_rows = tokens * topk / local_experts;  // expected rows per expert picks the kernel variant
   mark_stage(0, s);
   if ((rc = launch_align(topk_ids, tokens * topk, expert_map, local_experts, sched, cap,
                          reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
@@ -354,16 +386,17 @@ static int moe_forward_16bit(int fp16, const void* hidden_states, const void* w1
   disp.vec_per_row = hidden / 8;
   disp.rows_out = reinterpret_cast<uint4*>(xg);
   disp.granule_done = reinterpret_cast<int*>(ws + l.granules);
-  disp.enabled = 1;
+  disp.granule_target = kDispatchWarpsPerCta;
+  disp.enabled = kDispatchFused;
   MB200_CHECK_CUDA(cudaMemsetAsync(disp.granule_done, 0, size_t(l.granule_bytes), s));
   mark_stage(2, s);
   if ((rc = run_gemm_stage(kGateUpSwiglu, xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, nullptr, act, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8), &disp, fp16, avg_rows))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 8), &disp, fp16))) return rc;
   mark_stage(3, s);
   if ((rc = run_gemm_stage(kDownWeighted, act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                            sched.mtile_prefix, sched.sorted_ids, topk_weights, y, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16, avg_rows))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16))) return rc;
   mark_stage(4, s);
   rc = launch_combine_bf16(y, sched.inverse, int(tokens), topk, hidden, reinterpret_cast<__nv_bfloat16*>(out), s, fp16);
   mark_stage(5, s);
@@ -462,8 +495,17 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
   if ((rc = launch_align(topk_ids, tokens * topk, expert_map, local_experts, sched, cap,
                          reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
   mark_stage(1, s);
-  if ((rc = launch_gather_quant_fp8(reinterpret_cast<const __nv_bfloat16*>(hidden_states), sched, local_experts,
-                                    topk, hidden, xq, xs_t, cap, s))) return rc;
+  // every token is quantised once (reference.py:143-145 quantises the k-fold replicated rows:
+  // the same bytes k times), then its e4m3 row and scales are gathered into the sorted slots
+  uint8_t* xq_tok = reinterpret_cast<uint8_t*>(ws + l.xq_tok);
+  float* xs_tok = reinterpret_cast<float*>(ws + l.xs_tok);
+  if ((rc = launch_group_quant_fp8(reinterpret_cast<const __nv_bfloat16*>(hidden_states), tokens, hidden, xq_tok,
+                                   xs_tok, hidden / 128, 0, s))) return rc;
+  PeerTable self_q{}, self_s{};
+  self_q.ptr[0] = xq_tok;
+  self_s.ptr[0] = xs_tok;
+  if ((rc = launch_gather_rows_peer_fp8(self_q, self_s, 0, 1, int(tokens), topk, sched, local_experts, hidden, xq,
+                                        xs_t, cap, s))) return rc;
   mark_stage(2, s);
   if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, xq, xs_t, cap, w1, w1_scale, local_experts, hidden, intermediate,
                                sched.counts, sched.mtile_prefix, sched.sorted_ids, nullptr, actq, acts_t, status,

@@ -110,20 +110,51 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Wait limit for every in-kernel wait.  A kernel that gives up writes
-// kDevWaitTimeout to the status word, raises the CTA's abort flag and leaves
-// through its normal teardown, so the context stays usable.
-constexpr uint64_t kWaitLimitNs = 4ull * 1000 * 1000 * 1000;
+// Every in-kernel wait is bounded.  The limit applies to ONE wait (the clock starts
+// when that wait first finds nothing to do), so it bounds lack of progress, not the
+// length of the launch.  A wait that gives up writes kDevWaitTimeout + site to the
+// status word (first failure wins), raises the CTA's abort flag and the kernel
+// leaves through its normal teardown, so the context stays usable.
+// Default limit; word 1 of the status block (milliseconds, 0 = default) overrides it.
+constexpr uint64_t kDefaultWaitLimitNs = 4ull * 1000 * 1000 * 1000;
 
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory, one per CTA
-  int* status;               // global status word (may be null)
-  uint64_t t0;
+  int* status;               // global status block (may be null): [0] status, [1] wait limit in ms
+  uint64_t limit_ns;
 };
 
-// Returns false when the wait was abandoned.
+__device__ __forceinline__ uint64_t wait_limit_ns(const int* status) {
+  const int ms = status ? __ldg(status + 1) : 0;
+  return ms > 0 ? uint64_t(ms) * 1000000ull : kDefaultWaitLimitNs;
+}
+
+// Bookkeeping of one bounded wait: call expired() every few hundred polls.
+struct WaitClock {
+  uint64_t begin = 0;
+  __device__ __forceinline__ bool expired(const WaitCtx& ctx) {
+    const uint64_t now = global_timer_ns();
+    if (begin == 0) { begin = now; return false; }
+    return now - begin > ctx.limit_ns;
+  }
+};
+
+__device__ __forceinline__ void wait_give_up(WaitCtx& ctx, int where) {
+  *ctx.abort_flag = 1;
+  if (ctx.status) atomicCAS(ctx.status, 0, kDevWaitTimeout + where);
+}
+
+// Warp-collective: all 32 lanes call it together and get the same answer (a lane
+// that saw the phase complete while another lane ran out of time would otherwise
+// leave the warp split).  Returns false when the wait was abandoned.
+__device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity, WaitCtx& ctx, int where);
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtx& ctx, int where) {
+  const bool ok = mbar_wait_lane(bar, parity, ctx, where);
+  return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity, WaitCtx& ctx, int where) {
   uint32_t spins = 0;
+  WaitClock clock;
   while (true) {
     uint32_t ok;
     asm volatile(
@@ -138,9 +169,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtx
     if (ok) return true;
     if ((++spins & 0x3FF) == 0) {
       if (*ctx.abort_flag) return false;
-      if (global_timer_ns() - ctx.t0 > kWaitLimitNs) {
-        *ctx.abort_flag = 1;
-        if (ctx.status) atomicCAS(ctx.status, 0, kDevWaitTimeout + where);
+      if (clock.expired(ctx)) {
+        wait_give_up(ctx, where);
         return false;
       }
     }
@@ -235,72 +265,6 @@ __device__ __forceinline__ void umma_fp8(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
-// ---- CTA pairs (cluster of two CTAs on one tcgen05.mma, cta_group::2) -------------
-// A kernel uses one cta_group for all of its tcgen05 instructions, so the pair
-// kernels use these instead of the wrappers above.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// 2-D tiled load into THIS CTA's shared memory whose completion bytes are counted on
-// an mbarrier that may live in the peer CTA (bar is a shared::cluster address).
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int c0, int c1,
-                                                 uint32_t bar_cluster) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
-}
-// Arrive on the mbarrier at this shared-memory offset in every CTA of `cta_mask`
-// once all tcgen05.mma issued so far by this thread have finished.
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(bar), "h"(cta_mask)
-      : "memory");
-}
-// M = 256 across the pair: each CTA supplies its own 128 rows of A and half of the
-// N rows of B from the same shared-memory offsets; each CTA's tensor memory receives
-// its 128 accumulator rows.  Issued by one thread of the pair's rank-0 CTA.
-__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                               uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 // 32 lanes x 16 consecutive fp32 columns of tensor memory -> 16 registers per
 // thread (thread i of the warp reads lane base+i).
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -314,6 +278,50 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread.  The load is
+// asynchronous: the registers hold the data only after tmem_ld_wait32 on the same array.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+// Waits for every tensor-memory load this thread has issued.  The array is named as an
+// in/out operand so that the compiler cannot move a use of it above the wait while an
+// independent load into ANOTHER array stays in flight across it.
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+// Two fp32 lanes per instruction (fma.rn.f32x2): acc = p * s + acc on register pairs.
+// Each lane is an IEEE fused multiply-add, bit-identical to fmaf.
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo), "r"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  uint32_t a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+  lo = __uint_as_float(a);
+  hi = __uint_as_float(b);
+}
+__device__ __forceinline__ void fma_f32x2(uint64_t& acc, uint64_t p, uint64_t s) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(p), "l"(s));
 }
 
 }  // namespace mb200

@@ -207,7 +207,8 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
     disp.vec_per_row = hidden / 8;
     disp.rows_out = reinterpret_cast<uint4*>(ws + l.xg);
     disp.granule_done = reinterpret_cast<int*>(ws + l.granules);
-    disp.enabled = 1;
+    disp.granule_target = kDispatchWarpsPerCta;
+  disp.enabled = kDispatchFused;
     MB200_CHECK_CUDA(cudaMemsetAsync(disp.granule_done, 0, size_t(l.granule_bytes), s));
   }
   mark_stage(2, s);
@@ -226,11 +227,11 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   } else {
     if ((rc = run_gemm_stage(kGateUpSwiglu, ws + l.xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, nullptr, ws + l.act, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 8), &disp, fp16, expected_local / local_experts))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 8), &disp, fp16))) return rc;
     mark_stage(3, s);
     if ((rc = run_gemm_stage(kDownWeighted, ws + l.act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, weights_all, y, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16, expected_local / local_experts))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16))) return rc;
   }
   mark_stage(4, s);
   if ((rc = launch_combine_bf16(y, sched.inverse, int(all_tokens), topk, hidden,

@@ -37,9 +37,8 @@
 // whether the accumulators are double-buffered (token box <= 128) are derived on
 // the device from the largest expert segment in the schedule, so one launch suits
 // a 1-token and an 8192-token batch.  Every wait is bounded.
-//
-// kPair (opt-in) runs every tile on a cluster of two CTAs with
-// tcgen05.mma.cta_group::2; see the kernel's comment.
+
+#include <atomic>
 
 #include "layer.cuh"
 
@@ -53,7 +52,7 @@ constexpr int kMaxStages = 8;
 constexpr int kTmemCols = 512;
 constexpr int kEpilogueWarps = 8;
 constexpr int kFirstEpilogueWarp = 2;
-constexpr int kDispatchWarps = 4;  // warps 10-13: fused dispatch (gate/up GEMM only)
+constexpr int kDispatchWarps = kDispatchWarpsPerCta;  // warps 10-13: fused dispatch (gate/up GEMM only)
 constexpr int kDispatchLoads = 14;  // 16-byte loads each dispatch lane keeps in flight
 constexpr int kFirstDispatchWarp = kFirstEpilogueWarp + kEpilogueWarps;
 constexpr int kThreads = (kFirstDispatchWarp + kDispatchWarps) * 32;
@@ -92,13 +91,12 @@ struct Geometry {
   int acc_bufs;     // 2 when both accumulators of a tile fit in 256 columns
 };
 
-__device__ __forceinline__ Geometry make_geometry(int max_blocks16, bool pair) {
+__device__ __forceinline__ Geometry make_geometry(int max_blocks16) {
   Geometry g;
   int rows = max_blocks16 * kPad;
   g.box_index = rows <= 16 ? 0 : rows <= 32 ? 1 : rows <= 64 ? 2 : rows <= 128 ? 3 : 4;
   g.tb_rows = 16 << g.box_index;
-  // a CTA of a pair holds half of the tile's token rows
-  g.stage_bytes = kWeightBytes + (pair ? g.tb_rows / 2 : g.tb_rows) * 128;
+  g.stage_bytes = kWeightBytes + g.tb_rows * 128;
   int s = int(kRingBytes) / g.stage_bytes;
   g.stages = s > kMaxStages ? kMaxStages : s;
   g.acc_bufs = g.tb_rows <= 128 ? 2 : 1;
@@ -155,13 +153,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-// kPair: two CTAs (a cluster of 2 on neighbouring SMs) share every tile.  Rank r of
-// the pair owns feature block 2p + r (its own 2 x 128 weight rows and its own
-// accumulators), loads only HALF of the tile's token rows, and one tcgen05.mma with
-// cta_group::2 issued by rank 0 multiplies both CTAs' weight rows with both halves of
-// the tokens: per CTA and K step 32 KB of weights + ntok/2 token rows enter shared
-// memory instead of 32 KB + ntok rows, which is what bounds large batches.
-template <int kMode, bool kPair>
+template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ TokenMaps maps_t, const GemmArgs args,
@@ -179,10 +171,8 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
   // the down GEMM has no dispatch: its warps 10-13 drain accumulators too
   constexpr int kEpiWarps = kMode == kDownWeighted ? kEpilogueWarps + kDispatchWarps : kEpilogueWarps;
   constexpr int kChunkStride = kEpiWarps / 4;  // warps per tensor-memory lane quarter
-  const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
-  const bool leader = cta_rank == 0;  // issues the MMAs, owns the full / acc_empty barriers
-  const int worker = kPair ? int(blockIdx.x >> 1) : int(blockIdx.x);   // tile stream of this CTA (pair)
-  const int workers = kPair ? int(gridDim.x >> 1) : int(gridDim.x);
+  const int worker = int(blockIdx.x);
+  const int workers = int(gridDim.x);
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&map_w);
@@ -192,7 +182,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tail->acc_full[b]), 1);
-      mbar_init(smem_u32(&tail->acc_empty[b]), kEpiWarps * (kPair ? 2 : 1));
+      mbar_init(smem_u32(&tail->acc_empty[b]), kEpiWarps);
     }
     mbar_init(smem_u32(&tail->epi_bar), kEpiWarps);
     tail->abort_flag = 0;
@@ -200,17 +190,11 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    if (kPair) {
-      tmem_alloc_pair(smem_u32(&tail->tmem_base), kTmemCols);
-      tmem_relinquish_pair();
-    } else {
-      tmem_alloc(smem_u32(&tail->tmem_base), kTmemCols);
-      tmem_relinquish();
-    }
+    tmem_alloc(smem_u32(&tail->tmem_base), kTmemCols);
+    tmem_relinquish();
   }
   for (int i = threadIdx.x; i <= E; i += kThreads) tail->prefix[i] = args.mtile_prefix[i];
   __syncthreads();
-  if (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
   // largest expert segment -> token box, stage geometry
   {
     int mx = 0;
@@ -226,7 +210,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     if (lane == 0 && mx > 0) atomicMax(&tail->max_blocks16, mx);
   }
   __syncthreads();
-  const Geometry geo = make_geometry(tail->max_blocks16, kPair);
+  const Geometry geo = make_geometry(tail->max_blocks16);
   // token blocks per expert, exclusive scan by warp 0 (each lane owns a run of experts)
   if (warp == 0) {
     const int blocks_per_tile = geo.tb_rows / kPad;
@@ -255,11 +239,10 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
 
   const unsigned long long probe_c0 = clock64(), probe_t0 = global_timer_ns();
   const uint32_t tmem_base = tail->tmem_base;
-  // a pair covers two feature blocks per tile
-  const int n_fgroups = kPair ? (args.n_tiles + 1) / 2 : args.n_tiles;
+  const int n_fgroups = args.n_tiles;
   const int total_tiles = tail->tb_prefix[E] * n_fgroups;
   const uint32_t acc1_off = geo.acc_bufs == 2 ? 128u : 256u;  // column of the second accumulator
-  WaitCtx ctx{&tail->abort_flag, args.status, global_timer_ns()};
+  WaitCtx ctx{&tail->abort_flag, args.status, wait_limit_ns(args.status)};
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -269,22 +252,24 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     bool ok = true;
     for (int tile = worker; ok && tile < total_tiles; tile += workers) {
       const TileCoord tc = decode_tile(tile, tail, args.counts, E, n_fgroups, geo.tb_rows);
-      const int fblock = kPair ? tc.fblock * 2 + int(cta_rank) : tc.fblock;
+      const int fblock = tc.fblock;
       const int w_row = tc.expert * args.b_rows_per_expert;
       if (kMode == kGateUpSwiglu && disp.enabled) {
         // all 16-row granules of this token block must have been dispatched
         const int g0 = tc.row0 / kPad, ng = tc.ntok / kPad;  // ng <= 16
         uint32_t spins = 0;
+        WaitClock clock;
         while (true) {
-          int v = kDispatchWarps;
+          int v = disp.granule_target;
           if (lane < ng)
             asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(disp.granule_done + g0 + lane) : "memory");
-          if (__all_sync(0xffffffffu, v >= kDispatchWarps)) break;
+          if (__all_sync(0xffffffffu, v >= disp.granule_target)) break;
           if ((++spins & 0x3F) == 0) {
-            if (*ctx.abort_flag) { ok = false; break; }
-            if (global_timer_ns() - ctx.t0 > kWaitLimitNs) {
-              *ctx.abort_flag = 1;
-              if (ctx.status) atomicCAS(ctx.status, 0, kDevWaitTimeout + 6);
+            // warp-uniform decisions: the lanes read the flag and the timer at slightly different moments
+            const bool aborted = __any_sync(0xffffffffu, *ctx.abort_flag != 0);
+            const bool late = __any_sync(0xffffffffu, clock.expired(ctx));
+            if (aborted || late) {
+              if (!aborted && lane == 0) wait_give_up(ctx, 6);
               ok = false;
               break;
             }
@@ -303,48 +288,23 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
           const uint32_t w_dst = ring_addr + stage * geo.stage_bytes;
           const uint32_t t_dst = w_dst + kWeightBytes;
           const int kcol = kb * 64;
-          if (!kPair) {
-            mbar_expect_tx(bar, uint32_t(kWeightBytes + tc.ntok * 128));
-            if (kMode == kGateUpSwiglu) {
-              tma_load_2d(w_dst, &map_w, kcol, w_row + fblock * 128, bar);
-              tma_load_2d(w_dst + kWeightBytes / 2, &map_w, kcol,
-                          w_row + args.b_half_offset + fblock * 128, bar);
-            } else {
-              tma_load_2d(w_dst, &map_w, kcol, w_row + fblock * 256, bar);
-            }
-            // exactly ntok token rows: one box per set bit of ntok/16 (largest first), so a
-            // 144-token tile moves 18 KB of tokens, not the 32 KB of the launch's largest box
-            const int nb16 = tc.ntok >> 4;
-            int r = 0;
-#pragma unroll
-            for (int b = kTokenBoxes - 1; b >= 0; --b) {
-              if (nb16 & (1 << b)) {
-                tma_load_2d(t_dst + uint32_t(r) * 128u, &maps_t.m[b], kcol, tc.row0 + r, bar);
-                r += 16 << b;
-              }
-            }
+          mbar_expect_tx(bar, uint32_t(kWeightBytes + tc.ntok * 128));
+          if (kMode == kGateUpSwiglu) {
+            tma_load_2d(w_dst, &map_w, kcol, w_row + fblock * 128, bar);
+            tma_load_2d(w_dst + kWeightBytes / 2, &map_w, kcol,
+                        w_row + args.b_half_offset + fblock * 128, bar);
           } else {
-            // both CTAs' bytes are counted on rank 0's barrier; rank 0 announces the total
-            const uint32_t lead_bar = map_to_cta(bar, 0);
-            if (leader) mbar_expect_tx(bar, uint32_t(2 * kWeightBytes + tc.ntok * 128));
-            if (kMode == kGateUpSwiglu) {
-              tma_load_2d_pair(w_dst, &map_w, kcol, w_row + fblock * 128, lead_bar);
-              tma_load_2d_pair(w_dst + kWeightBytes / 2, &map_w, kcol,
-                               w_row + args.b_half_offset + fblock * 128, lead_bar);
-            } else {
-              tma_load_2d_pair(w_dst, &map_w, kcol, w_row + fblock * 256, lead_bar);
-            }
-            // this CTA's half of the token rows; the pair's token maps have boxes of 8 << b rows
-            const int half = tc.ntok >> 1;
-            const int nb8 = half >> 3;
-            int r = 0;
+            tma_load_2d(w_dst, &map_w, kcol, w_row + fblock * 256, bar);
+          }
+          // exactly ntok token rows: one box per set bit of ntok/16 (largest first), so a
+          // 144-token tile moves 18 KB of tokens, not the 32 KB of the launch's largest box
+          const int nb16 = tc.ntok >> 4;
+          int r = 0;
 #pragma unroll
-            for (int b = kTokenBoxes - 1; b >= 0; --b) {
-              if (nb8 & (1 << b)) {
-                tma_load_2d_pair(t_dst + uint32_t(r) * 128u, &maps_t.m[b], kcol,
-                                 tc.row0 + int(cta_rank) * half + r, lead_bar);
-                r += 8 << b;
-              }
+          for (int b = kTokenBoxes - 1; b >= 0; --b) {
+            if (nb16 & (1 << b)) {
+              tma_load_2d(t_dst + uint32_t(r) * 128u, &maps_t.m[b], kcol, tc.row0 + r, bar);
+              r += 16 << b;
             }
           }
         }
@@ -358,35 +318,19 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     uint32_t phase = 0;
     uint32_t it = 0;
     bool ok = true;
-#ifdef MB200_PROBE_WAITS
-    long long wait_full = 0, wait_acc = 0, c_start = clock64();
-#endif
-    // in a pair only rank 0 issues MMAs (for both CTAs)
-    for (int tile = worker; ok && leader && tile < total_tiles; tile += workers, ++it) {
+    for (int tile = worker; ok && tile < total_tiles; tile += workers, ++it) {
       const TileCoord tc = decode_tile(tile, tail, args.counts, E, n_fgroups, geo.tb_rows);
       const uint32_t buf = geo.acc_bufs == 2 ? (it & 1) : 0;
       const uint32_t use = geo.acc_bufs == 2 ? (it >> 1) : it;
-#ifdef MB200_PROBE_WAITS
-      long long c_a = clock64();
-#endif
       ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), (use & 1) ^ 1, ctx, 2);
-#ifdef MB200_PROBE_WAITS
-      wait_acc += clock64() - c_a;
-#endif
       if (!ok) break;
       tc_fence_after();
       const uint32_t d0 = tmem_base + buf * 256;
       const uint32_t d1 = d0 + acc1_off;
       const uint32_t fmt = args.fp16 ? 0u : 1u;  // kind::f16 operand format: 0 = f16, 1 = bf16
-      const uint32_t idesc = make_idesc(fmt, fmt, kPair ? 256 : 128, uint32_t(tc.ntok));
+      const uint32_t idesc = make_idesc(fmt, fmt, 128, uint32_t(tc.ntok));
       for (int kb = 0; kb < args.k_iters; ++kb) {
-#ifdef MB200_PROBE_WAITS
-        long long c_f = clock64();
-#endif
         ok = mbar_wait(smem_u32(&tail->full[stage]), phase, ctx, 3);
-#ifdef MB200_PROBE_WAITS
-        wait_full += clock64() - c_f;
-#endif
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
@@ -398,38 +342,21 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
           for (int k = 0; k < 4; ++k) {
             // 16 bf16 = 32 bytes of K per instruction: +2 in the 16-byte address field
             const uint32_t accumulate = (kb | k) != 0;
-            if (kPair) {
-              umma_bf16_pair(d0, w0_desc + 2 * k, t_desc + 2 * k, idesc, accumulate);
-              umma_bf16_pair(d1, w1_desc + 2 * k, t_desc + 2 * k, idesc, accumulate);
-            } else {
-              umma_bf16(d0, w0_desc + 2 * k, t_desc + 2 * k, idesc, accumulate);
-              umma_bf16(d1, w1_desc + 2 * k, t_desc + 2 * k, idesc, accumulate);
-            }
+            umma_bf16(d0, w0_desc + 2 * k, t_desc + 2 * k, idesc, accumulate);
+            umma_bf16(d1, w1_desc + 2 * k, t_desc + 2 * k, idesc, accumulate);
           }
-          // the stage is free in both CTAs once these MMAs have read it
-          if (kPair) tc_commit_pair(smem_u32(&tail->empty[stage]), 3);
-          else tc_commit(smem_u32(&tail->empty[stage]));
+          // the stage is free once these MMAs have read it
+          tc_commit(smem_u32(&tail->empty[stage]));
         }
         __syncwarp();
         if (++stage == geo.stages) { stage = 0; phase ^= 1; }
       }
-      if (ok && lane == 0) {
-        if (kPair) tc_commit_pair(smem_u32(&tail->acc_full[buf]), 3);
-        else tc_commit(smem_u32(&tail->acc_full[buf]));
-      }
+      if (ok && lane == 0) tc_commit(smem_u32(&tail->acc_full[buf]));
       __syncwarp();
     }
-#ifdef MB200_PROBE_WAITS
-    // diagnostic build only: cycles the MMA warp of CTA 0 waited for data / for a free accumulator
-    if (lane == 0 && blockIdx.x == 0 && args.clock_probe) {
-      args.clock_probe[4 + 3 * kMode] = wait_full;
-      args.clock_probe[5 + 3 * kMode] = wait_acc;
-      args.clock_probe[6 + 3 * kMode] = clock64() - c_start;
-    }
-#endif
   } else if (kMode == kGateUpSwiglu && warp >= kFirstDispatchWarp) {
     // ---------------- fused dispatch (gate/up GEMM): fill the sorted row buffer ----------------
-    if (kMode == kGateUpSwiglu && disp.enabled) {
+    if (kMode == kGateUpSwiglu && disp.enabled == kDispatchFused) {
       const int dw = warp - kFirstDispatchWarp;
       const int granules = tail->prefix[E];
       for (int g = blockIdx.x; g < granules; g += gridDim.x) {
@@ -473,7 +400,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
     bool ok = true;
     for (int tile = worker; ok && tile < total_tiles; tile += workers, ++it) {
       const TileCoord tc = decode_tile(tile, tail, args.counts, E, n_fgroups, geo.tb_rows);
-      const int fblock = kPair ? tc.fblock * 2 + int(cta_rank) : tc.fblock;
+      const int fblock = tc.fblock;
       const uint32_t buf = geo.acc_bufs == 2 ? (it & 1) : 0;
       const uint32_t use = geo.acc_bufs == 2 ? (it >> 1) : it;
       const int par = it & 1;
@@ -510,11 +437,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
         // every value of this warp's share is in registers: the accumulator may be overwritten
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          // the MMA issuer (rank 0 of a pair) waits for the epilogue warps of both CTAs
-          if (kPair) mbar_arrive_cluster(map_to_cta(smem_u32(&tail->acc_empty[buf]), 0));
-          else mbar_arrive(smem_u32(&tail->acc_empty[buf]));
-        }
+        if (lane == 0) mbar_arrive(smem_u32(&tail->acc_empty[buf]));
         released = true;
       };
       if (kMode == kGateUpSwiglu) {
@@ -599,8 +522,6 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
-  // the peer may still be reading this CTA's shared memory or signalling its barriers
-  if (kPair) cluster_sync_all();
   if (threadIdx.x == 0 && blockIdx.x == 0 && args.clock_probe) {
     // lets a benchmark read the SM clock the kernel really ran at (cycles / ns)
     args.clock_probe[0] = clock64() - probe_c0;
@@ -613,104 +534,38 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       // the shared memory is handed to the next CTA.
       for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
-    if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
-    else tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
 using KernelFn = void (*)(const CUtensorMap, const TokenMaps, const GemmArgs, const FusedDispatch);
 
-KernelFn pick_kernel(GemmMode mode, bool pair) {
-  if (mode == kGateUpSwiglu)
-    return pair ? grouped_gemm_bf16_kernel<kGateUpSwiglu, true> : grouped_gemm_bf16_kernel<kGateUpSwiglu, false>;
-  return pair ? grouped_gemm_bf16_kernel<kDownWeighted, true> : grouped_gemm_bf16_kernel<kDownWeighted, false>;
-}
-
 }  // namespace
-
-// How many CTA pairs (clusters of 2) of the pair kernel the device runs at once; 0 when
-// the device cannot co-schedule them.  Queried once per device.
-int grouped_gemm_pair_capacity(int device) {
-  static int cached[64];
-  static bool known[64] = {};
-  if (device < 0 || device >= 64) return 0;
-  if (known[device]) return cached[device];
-  int sms = 0, clusters = 0;
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-  for (int m = 0; m < 2; ++m) {
-    KernelFn k = pick_kernel(GemmMode(m), true);
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)) != cudaSuccess) {
-      cudaGetLastError();
-      known[device] = true;
-      return cached[device] = 0;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(sms / 2 * 2));
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<void*>(k), &cfg) != cudaSuccess) {
-      cudaGetLastError();
-      n = 0;
-    }
-    if (n > sms / 2) n = sms / 2;
-    clusters = m == 0 ? n : (n < clusters ? n : clusters);
-  }
-  known[device] = true;
-  return cached[device] = clusters;
-}
 
 int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
                              const GemmArgs& args, const FusedDispatch& dispatch, int device,
-                             cudaStream_t stream, bool pair) {
+                             cudaStream_t stream) {
   MB200_REQUIRE(args.num_experts >= 1 && args.num_experts <= kMaxExperts, kUnsupportedShape,
                 "grouped_gemm: %d local experts, supported 1..%d", args.num_experts, kMaxExperts);
   MB200_REQUIRE(!dispatch.enabled || mode == kGateUpSwiglu, kInvalidArgument,
                 "grouped_gemm: fused dispatch belongs to the gate/up stage");
   MB200_REQUIRE((reinterpret_cast<uintptr_t>(args.out) & 15) == 0 && args.out_cols % 8 == 0, kInvalidArgument,
                 "grouped_gemm: output must be 16-byte aligned with a row length that is a multiple of 8");
-  static bool configured[64][2] = {};
-  int sms = 0;
-  MB200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  void* params[] = {const_cast<CUtensorMap*>(&map_w), const_cast<TokenMaps*>(&maps_t),
-                    const_cast<GemmArgs*>(&args), const_cast<FusedDispatch*>(&dispatch)};
-  if (pair) {
-    const int clusters = grouped_gemm_pair_capacity(device);  // also sets the shared-memory attribute
-    MB200_REQUIRE(clusters > 0, kCudaError, "grouped_gemm: this device cannot co-schedule CTA pairs");
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(2 * clusters));
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    // all CTAs resident (the fused dispatch needs it), as in the single-CTA launch below
-    attr[1].id = cudaLaunchAttributeCooperative;
-    attr[1].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = dispatch.enabled ? 2 : 1;
-    MB200_CHECK_CUDA(cudaLaunchKernelExC(&cfg, reinterpret_cast<void*>(pick_kernel(mode, true)), params));
-    return kOk;
+  KernelFn kernel = mode == kGateUpSwiglu ? grouped_gemm_bf16_kernel<kGateUpSwiglu>
+                                          : grouped_gemm_bf16_kernel<kDownWeighted>;
+  // once per device and kernel; a second thread that sets it again does no harm
+  static std::atomic<bool> configured[kMaxDevices][2];
+  if (device < 0 || device >= kMaxDevices || !configured[device][mode].load(std::memory_order_acquire)) {
+    MB200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+    if (device >= 0 && device < kMaxDevices) configured[device][mode].store(true, std::memory_order_release);
   }
-  KernelFn kernel = pick_kernel(mode, false);
-  if (device >= 0 && device < 64 && !configured[device][mode]) {
-    MB200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          int(kSmemBytes)));
-    configured[device][mode] = true;
-  }
-  if (dispatch.enabled) {
+  const int sms = device_sm_count(device);
+  MB200_REQUIRE(sms > 0, kCudaError, "grouped_gemm: cannot read the SM count of device %d", device);
+  if (dispatch.enabled == kDispatchFused) {
     // the tile loader waits for rows that other CTAs' dispatch warps deliver: all
     // CTAs must be resident, which a cooperative launch guarantees (or refuses)
+    void* params[] = {const_cast<CUtensorMap*>(&map_w), const_cast<TokenMaps*>(&maps_t),
+                      const_cast<GemmArgs*>(&args), const_cast<FusedDispatch*>(&dispatch)};
     MB200_CHECK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(sms), dim3(kThreads),
                                                  params, kSmemBytes, stream));
   } else {

@@ -25,6 +25,8 @@
 //   down:     columns = 128 outputs = one weight scale block; scaled by the
 //             combine weight and stored as bf16 at the row's flat assignment.
 
+#include <atomic>
+
 #include "layer.cuh"
 
 namespace mb200 {
@@ -38,7 +40,14 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = (2 + kEpilogueWarps) * 32;
+constexpr int kFirstEpilogueWarp = 4;  // warps 0-3: one warpgroup of helpers (TMA, MMA, two spare)
+constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
+// Registers per thread after the warpgroups re-split the register file (setmaxnreg): the
+// epilogue threads hold 128 accumulators + two 32-register load buffers, the helpers need few.
+// 128 * helper + 256 * epilogue <= 65536.  The split is per kernel: these are the ones the
+// compiler fits without spilling (gate/up: 64 + 216, down: 80 + 208).
+template <int kMode> struct RegSplit { static constexpr int kHelper = 64, kEpilogue = 216; };
+template <> struct RegSplit<kDownWeighted> { static constexpr int kHelper = 80, kEpilogue = 208; };
 constexpr int kMaxKBlocks = 128;  // K up to 16384
 
 struct SmemTail {
@@ -146,8 +155,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t tmem_base = tail->tmem_base;
   const int total_tiles = tail->prefix[args.num_experts] * args.n_tiles;
   const int k_blocks = args.k_blocks;
-  WaitCtx ctx{&tail->abort_flag, args.status, global_timer_ns()};
+  WaitCtx ctx{&tail->abort_flag, args.status, wait_limit_ns(args.status)};
 
+  // Each role's code sits inside the branch that re-sizes its warpgroup's registers, so the
+  // compiler knows which budget applies where.
+  if (warp < kFirstEpilogueWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(RegSplit<kMode>::kHelper));
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     int stage = 0;
@@ -208,13 +221,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(RegSplit<kMode>::kEpilogue));
     // ---------------- epilogue: promote partials, then finish the tile ----------------
-    const int ew = warp - 2;
+    const int ew = warp - kFirstEpilogueWarp;
     const int quarter = warp & 3;
     const int half = ew >> 2;
     const int r = quarter * 32 + lane;
-    const int etid = threadIdx.x - 64;
+    const int etid = threadIdx.x - kFirstEpilogueWarp * 32;
     uint32_t pit = 0;
     uint32_t it = 0;
     uint32_t epi_phase = 0;
@@ -238,10 +253,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
       const int row = tc.row0 + r;
       const bool row_ok = r < tc.valid_rows;
       const float* a_scale = args.a_scale_t + row;  // [kb][row_capacity]
-      float acc[128];
+      // 128 fp32 accumulators per thread, kept as register pairs for fma.rn.f32x2:
+      //   gate/up: pairs 0..31 = this thread's 64 gate columns, 32..63 = the matching up columns
+      //   down:    pairs 0..63 = 128 consecutive output columns
+      uint64_t acc[64];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+      for (int i = 0; i < 64; ++i) acc[i] = 0ull;
       float a_s_next = __ldg(a_scale);
+      // tensor-memory column of this thread's four 32-column chunks
+      const uint32_t col0 = kMode == kGateUpSwiglu ? uint32_t(half * 64) : uint32_t(half * 128);
+      const uint32_t col2 = kMode == kGateUpSwiglu ? uint32_t(128 + half * 64) : uint32_t(half * 128 + 64);
 
       for (int kb = 0; kb < k_blocks; ++kb, ++pit) {
         const uint32_t pbuf = pit & 1;
@@ -251,72 +272,70 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         const float a_s = a_s_next;
         if (kb + 1 < k_blocks) a_s_next = __ldg(a_scale + size_t(kb + 1) * args.row_capacity);
         const uint32_t taddr = tmem_base + pbuf * kAccCols + (uint32_t(quarter * 32) << 16);
-        if (kMode == kGateUpSwiglu) {
-          const float sg = a_s * tail->wscale[par][0][kb];
-          const float su = a_s * tail->wscale[par][1][kb];
+        // scale of the first two chunks and of the last two (gate / up weight blocks differ)
+        const float s_lo = a_s * tail->wscale[par][kMode == kGateUpSwiglu ? 0 : half][kb];
+        const float s_hi = kMode == kGateUpSwiglu ? a_s * tail->wscale[par][1][kb] : s_lo;
+        const uint64_t s01 = pack_f32x2(__float_as_uint(s_lo), __float_as_uint(s_lo));
+        const uint64_t s23 = pack_f32x2(__float_as_uint(s_hi), __float_as_uint(s_hi));
+        // Promotion acc += partial * scale, software-pipelined: the tensor-memory load of
+        // chunk c+1 is in flight while chunk c is folded in.
+        uint32_t pa[32], pb[32];
+        tmem_ld32(taddr + col0, pa);
+        tmem_ld_wait32(pa);
+        tmem_ld32(taddr + col0 + 32, pb);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t g[16], u[16];
-            tmem_ld16(taddr + half * 64 + c * 16, g);
-            tmem_ld16(taddr + 128 + half * 64 + c * 16, u);
-            tmem_ld_wait();
+        for (int j = 0; j < 16; ++j) fma_f32x2(acc[j], pack_f32x2(pa[2 * j], pa[2 * j + 1]), s01);
+        tmem_ld_wait32(pb);
+        tmem_ld32(taddr + col2, pa);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              acc[c * 16 + j] = fmaf(__uint_as_float(g[j]), sg, acc[c * 16 + j]);
-              acc[64 + c * 16 + j] = fmaf(__uint_as_float(u[j]), su, acc[64 + c * 16 + j]);
-            }
-          }
-        } else {
-          const float s = a_s * tail->wscale[par][half][kb];
+        for (int j = 0; j < 16; ++j) fma_f32x2(acc[16 + j], pack_f32x2(pb[2 * j], pb[2 * j + 1]), s01);
+        tmem_ld_wait32(pa);
+        tmem_ld32(taddr + col2 + 32, pb);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v0[16], v1[16];
-            tmem_ld16(taddr + half * 128 + c * 32, v0);
-            tmem_ld16(taddr + half * 128 + c * 32 + 16, v1);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              acc[c * 32 + j] = fmaf(__uint_as_float(v0[j]), s, acc[c * 32 + j]);
-              acc[c * 32 + 16 + j] = fmaf(__uint_as_float(v1[j]), s, acc[c * 32 + 16 + j]);
-            }
-          }
-        }
+        for (int j = 0; j < 16; ++j) fma_f32x2(acc[32 + j], pack_f32x2(pa[2 * j], pa[2 * j + 1]), s23);
+        tmem_ld_wait32(pb);
+        // the whole partial is in registers: hand the buffer back before the last 32 columns are folded in
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&tail->part_empty[pbuf]));
+#pragma unroll
+        for (int j = 0; j < 16; ++j) fma_f32x2(acc[48 + j], pack_f32x2(pb[2 * j], pb[2 * j + 1]), s23);
       }
       if (!ok) break;
 
       if (kMode == kGateUpSwiglu) {
         // SiLU(gate)*up, rounded to bf16 as the reference does before re-quantising
+        float v[64];
         float amax = 0.f;
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const float g = acc[j];
-          const float v = bf16_round(g / (1.0f + __expf(-g)) * acc[64 + j]);
-          acc[j] = v;
-          amax = fmaxf(amax, fabsf(v));
+        for (int j = 0; j < 32; ++j) {
+          float g0, g1, u0, u1;
+          unpack_f32x2(acc[j], g0, g1);
+          unpack_f32x2(acc[32 + j], u0, u1);
+          v[2 * j] = bf16_round(g0 / (1.0f + __expf(-g0)) * u0);
+          v[2 * j + 1] = bf16_round(g1 / (1.0f + __expf(-g1)) * u1);
+          amax = fmaxf(amax, fmaxf(fabsf(v[2 * j]), fabsf(v[2 * j + 1])));
         }
         tail->amax[half][r] = amax;
         ok = epilogue_barrier(&tail->epi_bar, epi_phase, ctx, lane);
         if (!ok) break;
         amax = fmaxf(fmaxf(amax, tail->amax[half ^ 1][r]), 1e-10f);
         const float scale = __fdiv_rn(amax, 448.0f);
-        const int col0 = tc.n_tile * 128 + half * 64;
-        if (row_ok && col0 < args.out_cols) {
-          uint8_t* dst = reinterpret_cast<uint8_t*>(args.out) + size_t(row) * args.out_cols + col0;
+        const int out_col0 = tc.n_tile * 128 + half * 64;
+        if (row_ok && out_col0 < args.out_cols) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(args.out) + size_t(row) * args.out_cols + out_col0;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int j = q * 16 + i * 4;
-              w[i] = pack_e4m3x4(fminf(fmaxf(__fdiv_rn(acc[j], scale), -448.f), 448.f),
-                                 fminf(fmaxf(__fdiv_rn(acc[j + 1], scale), -448.f), 448.f),
-                                 fminf(fmaxf(__fdiv_rn(acc[j + 2], scale), -448.f), 448.f),
-                                 fminf(fmaxf(__fdiv_rn(acc[j + 3], scale), -448.f), 448.f));
+              w[i] = pack_e4m3x4(fminf(fmaxf(__fdiv_rn(v[j], scale), -448.f), 448.f),
+                                 fminf(fmaxf(__fdiv_rn(v[j + 1], scale), -448.f), 448.f),
+                                 fminf(fmaxf(__fdiv_rn(v[j + 2], scale), -448.f), 448.f),
+                                 fminf(fmaxf(__fdiv_rn(v[j + 3], scale), -448.f), 448.f));
             }
-            if (col0 + q * 16 < args.out_cols)
+            if (out_col0 + q * 16 < args.out_cols)
               reinterpret_cast<uint4*>(dst)[q] = make_uint4(w[0], w[1], w[2], w[3]);
           }
           if (half == 0) args.out_scale_t[size_t(tc.n_tile) * args.row_capacity + row] = scale;
@@ -328,17 +347,18 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
           assignment = __ldg(args.sorted_ids + row);
           if (assignment >= 0) w = __ldg(args.row_scale + assignment);
         }
-        const int col0 = tc.n_tile * 256 + half * 128;
+        const int out_col0 = tc.n_tile * 256 + half * 128;
         if (assignment >= 0) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.out) + size_t(assignment) * args.out_cols + col0;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.out) + size_t(assignment) * args.out_cols + out_col0;
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
-            if (col0 + q * 8 < args.out_cols) {
+            if (out_col0 + q * 8 < args.out_cols) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) unpack_f32x2(acc[q * 4 + i], f[2 * i], f[2 * i + 1]);
               reinterpret_cast<uint4*>(dst)[q] =
-                  make_uint4(pack_bf16x2(w * acc[q * 8], w * acc[q * 8 + 1]),
-                             pack_bf16x2(w * acc[q * 8 + 2], w * acc[q * 8 + 3]),
-                             pack_bf16x2(w * acc[q * 8 + 4], w * acc[q * 8 + 5]),
-                             pack_bf16x2(w * acc[q * 8 + 6], w * acc[q * 8 + 7]));
+                  make_uint4(pack_bf16x2(w * f[0], w * f[1]), pack_bf16x2(w * f[2], w * f[3]),
+                             pack_bf16x2(w * f[4], w * f[5]), pack_bf16x2(w * f[6], w * f[7]));
             }
           }
         }
@@ -373,15 +393,16 @@ int launch_grouped_gemm_fp8(GemmMode mode, const CUtensorMap& map_a, const CUten
                 "grouped_gemm_fp8: %d K blocks of 128, supported 1..%d", args.k_blocks, kMaxKBlocks);
   MB200_REQUIRE(args.out_cols % 16 == 0, kUnsupportedShape,
                 "grouped_gemm_fp8: output row length %d must be a multiple of 16", args.out_cols);
-  static bool configured[64][2] = {};
-  int sms = 0;
-  MB200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  const int sms = device_sm_count(device);
+  MB200_REQUIRE(sms > 0, kCudaError, "grouped_gemm_fp8: cannot read the SM count of device %d", device);
   auto kernel = mode == kGateUpSwiglu ? grouped_gemm_fp8_kernel<kGateUpSwiglu>
                                       : grouped_gemm_fp8_kernel<kDownWeighted>;
-  if (device >= 0 && device < 64 && !configured[device][mode]) {
+  // once per device and kernel; a second thread that sets it again does no harm
+  static std::atomic<bool> configured[kMaxDevices][2];
+  if (device < 0 || device >= kMaxDevices || !configured[device][mode].load(std::memory_order_acquire)) {
     MB200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           int(kSmemBytes)));
-    configured[device][mode] = true;
+    if (device >= 0 && device < kMaxDevices) configured[device][mode].store(true, std::memory_order_release);
   }
   kernel<<<sms, kThreads, kSmemBytes, stream>>>(map_a, map_b, args);
   MB200_CHECK_CUDA(cudaGetLastError());

@@ -28,6 +28,8 @@
 // warp w reads lanes 32*(w%4).. (one feature row per thread) and the 16-column
 // chunks of parity (w-2)/4, at most 64 columns x 2 accumulators per thread.
 
+#include <atomic>
+
 #include "layer.cuh"
 
 namespace mb200 {
@@ -208,7 +210,7 @@ grouped_gemm_fp8_cols_kernel(const __grid_constant__ CUtensorMap map_w,
   const unsigned long long probe_c0 = clock64(), probe_t0 = global_timer_ns();
   const uint32_t tmem_base = tail->tmem_base;
   const int total_tiles = tail->tb_prefix[E] * args.n_tiles;
-  WaitCtx ctx{&tail->abort_flag, args.status, global_timer_ns()};
+  WaitCtx ctx{&tail->abort_flag, args.status, wait_limit_ns(args.status)};
 
   if (warp == 0) {
     // ---------------- TMA producer: one stage = one 128-deep K block ----------------
@@ -447,15 +449,16 @@ int launch_grouped_gemm_fp8_cols(GemmMode mode, const CUtensorMap& map_w, const 
                 "grouped_gemm_fp8: %d local experts, supported 1..%d", args.num_experts, kMaxExperts);
   MB200_REQUIRE(args.k_blocks >= 1 && args.k_blocks <= kMaxKBlocks, kUnsupportedShape,
                 "grouped_gemm_fp8: %d K blocks of 128, supported 1..%d", args.k_blocks, kMaxKBlocks);
-  static bool configured[64][2] = {};
-  int sms = 0;
-  MB200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  const int sms = device_sm_count(device);
+  MB200_REQUIRE(sms > 0, kCudaError, "grouped_gemm_fp8: cannot read the SM count of device %d", device);
   auto kernel = mode == kGateUpSwiglu ? grouped_gemm_fp8_cols_kernel<kGateUpSwiglu>
                                       : grouped_gemm_fp8_cols_kernel<kDownWeighted>;
-  if (device >= 0 && device < 64 && !configured[device][mode]) {
+  // once per device and kernel; a second thread that sets it again does no harm
+  static std::atomic<bool> configured[kMaxDevices][2];
+  if (device < 0 || device >= kMaxDevices || !configured[device][mode].load(std::memory_order_acquire)) {
     MB200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           int(kSmemBytes)));
-    configured[device][mode] = true;
+    if (device >= 0 && device < kMaxDevices) configured[device][mode].store(true, std::memory_order_release);
   }
   kernel<<<sms, kThreads, kSmemBytes, stream>>>(map_w, maps_t, args);
   MB200_CHECK_CUDA(cudaGetLastError());

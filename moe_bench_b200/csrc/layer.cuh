@@ -11,6 +11,10 @@ constexpr int kTileM = 128;        // fp8 path: rows per M tile; expert segments
 constexpr int kPadBf16 = 16;       // bf16 path: expert segments are padded to 16 rows
 constexpr int kMaxExperts = 1024;  // local experts per rank supported by the kernels
 
+constexpr int kMaxDevices = 64;    // device ordinals the per-device caches cover
+// SM count of a device, cached (thread-safe); 0 if it cannot be read.
+int device_sm_count(int device);
+
 constexpr int kMaxPeers = 16;
 struct PeerTable {
   void* ptr[kMaxPeers];  // one pointer per rank, valid in this process
@@ -41,10 +45,6 @@ int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, 
 // Per-row, per-128-group e4m3 quantisation.  scales_t is [K/128][scale_ld] (group-major).
 int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uint8_t* q,
                            float* scales, int64_t scale_ld, int transposed, cudaStream_t stream);
-// Gather + quantise: xq[row] = e4m3(x[token(row)]), scales_t[g][row] for the sorted rows.
-int launch_gather_quant_fp8(const __nv_bfloat16* x, const Schedule& sched, int local_experts,
-                            int topk, int hidden, uint8_t* xq, float* scales_t,
-                            int64_t row_capacity, cudaStream_t stream);
 
 // ---- grouped_gemm.cu -----------------------------------------------------------------
 struct GemmArgs {
@@ -76,26 +76,23 @@ struct FusedDispatch {
   int vec_per_row;        // hidden / 8 (16-byte vectors per row)
   uint4* rows_out;        // sorted row buffer the GEMM's token operand is loaded from
   int* granule_done;      // [row_capacity / 16] arrival counters, zeroed before the launch
-  int enabled;
+  int granule_target;     // a granule is complete when its counter reaches this value
+  int enabled;            // kDispatchOff, kDispatchFused or kDispatchExternal
 };
+// kDispatchFused: this kernel's dispatch warps fill the rows (counter target = their number).
+// kDispatchExternal: someone else fills the rows and raises the counters (another kernel, or a
+// peer GPU's push); the kernel only waits for them.
+enum DispatchMode : int { kDispatchOff = 0, kDispatchFused = 1, kDispatchExternal = 2 };
+constexpr int kDispatchWarpsPerCta = 4;
 // Token-operand tensor maps with boxes of 16, 32, 64, 128 and 256 rows; the
 // kernel picks one from the largest expert segment it finds in the schedule.
 constexpr int kTokenBoxes = 5;
 struct TokenMaps {
   CUtensorMap m[kTokenBoxes];
 };
-// pair: the CTA-pair kernel (cta_group::2); maps_t then holds boxes of 8 << i rows
-// instead of 16 << i.
 int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
                              const GemmArgs& args, const FusedDispatch& dispatch, int device,
-                             cudaStream_t stream, bool pair);
-int grouped_gemm_pair_capacity(int device);
-// Rows per expert from which the 16-bit GEMMs run as CTA pairs; 0 = never.  Off by
-// default: in interleaved A/B runs at 8192 tokens the pair kernel, bit-identical in
-// its results, needed the same SM cycles as the single-CTA kernel (both are bound by
-// shared-memory bandwidth: tcgen05.mma operand reads plus the TMA fill), so it buys
-// nothing yet.  The environment variable MB200_PAIR_MIN_ROWS (read once) overrides it.
-constexpr int kPairMinAvgRows = 0;
+                             cudaStream_t stream);
 
 // grouped_gemm_fp8.cu: e4m3 operands, fp32 block scales applied in the epilogue
 struct GemmFp8Args {
@@ -148,6 +145,7 @@ int launch_reduce_partials(const PeerTable& partial, int rank, int world, int to
 struct Layout {
   int64_t status, counts, prefix, sorted, inverse, scratch, xg, act, y, total;
   int64_t xs, acts;  // fp8 only: transposed activation scales [K/128][cap], [N/128][cap]
+  int64_t xq_tok, xs_tok;  // fp8 only: the tokens quantised once, [T][K] e4m3 and [T][K/128] scales
   int64_t granules;  // bf16 only: arrival counter per 16-row granule of the sorted row buffer
   int64_t granule_bytes;
 };
@@ -162,7 +160,7 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
                    unsigned long long* clock_probe = nullptr, const FusedDispatch* dispatch = nullptr,
-                   int fp16 = 0, int64_t avg_rows = 0);
+                   int fp16 = 0);
 int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,

@@ -34,6 +34,7 @@ namespace mb200 {
 namespace {
 
 constexpr uint64_t kBarrierLimitNs = 3ull * 1000 * 1000 * 1000;
+constexpr int kGatherLoads = 7;  // 16-byte loads a lane of the row gather keeps in flight
 
 __global__ void peer_barrier_kernel(PeerTable flags, int rank, int world, uint32_t seq, int* status) {
   const int peer = threadIdx.x;
@@ -111,7 +112,16 @@ __global__ void gather_rows_peer_fp8_kernel(PeerTable xq, PeerTable xs, int rank
     const uint4* src = reinterpret_cast<const uint4*>(xq.ptr[src_rank]) + int64_t(t) * vec_per_row;
     const float* src_s = reinterpret_cast<const float*>(xs.ptr[src_rank]) + int64_t(t) * groups_per_row;
     uint4* dst = out_q + row * vec_per_row;
-    for (int v = lane; v < vec_per_row; v += 32) dst[v] = src[v];
+    // kGatherLoads 16-byte loads in flight per lane (a load over NVLink takes microseconds)
+    for (int v0 = lane; v0 < vec_per_row; v0 += 32 * kGatherLoads) {
+      uint4 buf[kGatherLoads];
+#pragma unroll
+      for (int u = 0; u < kGatherLoads; ++u)
+        if (v0 + u * 32 < vec_per_row) buf[u] = src[v0 + u * 32];
+#pragma unroll
+      for (int u = 0; u < kGatherLoads; ++u)
+        if (v0 + u * 32 < vec_per_row) dst[v0 + u * 32] = buf[u];
+    }
     for (int g = lane; g < groups_per_row; g += 32) out_scales_t[int64_t(g) * row_capacity + row] = src_s[g];
   }
 }
@@ -160,7 +170,7 @@ __global__ void reduce_partials_kernel(PeerTable partial, int rank, int world, i
 
 int grid_for_rows(int64_t items, int threads, int waves) {
   int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaGetDevice(&dev) == cudaSuccess && device_sm_count(dev) > 0) sms = device_sm_count(dev);
   int64_t blocks = (items + threads - 1) / threads;
   const int64_t cap = int64_t(sms) * waves;
   if (blocks > cap) blocks = cap;

@@ -1,8 +1,4 @@
 // Row-wise, bandwidth-bound stages around the grouped GEMMs:
-//   gather_quant:  fp8 path: xq[row, :] = e4m3(x[token(row), :]) for the sorted
-//                  assignment rows (the reference replicates every token k times
-//                  instead, reference.py:130-145).  The bf16 path gathers inside
-//                  the gate/up GEMM kernel.
 //   combine:       out[t, :] = sum over the k local assignments of token t of
 //                  the already weighted rows y[t*k + j, :], fp32 sum, bf16 store
 //                  (reference.py:180-182).
@@ -99,39 +95,6 @@ __global__ void group_quant_fp8_kernel(const uint4* __restrict__ x, int64_t rows
   }
 }
 
-// Sorted rows: gather the token's row and quantise it in one pass (one warp per
-// row, four groups per step).  Scales are stored group-major so the GEMM's
-// epilogue threads (one row each) read them coalesced.
-__global__ void gather_quant_fp8_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted_ids,
-                                        const int* __restrict__ mtile_prefix, int local_experts,
-                                        int topk, int groups_per_row, uint2* __restrict__ xq,
-                                        float* __restrict__ scales_t, int64_t row_capacity, int pad) {
-  int64_t rows = int64_t(__ldg(mtile_prefix + local_experts)) * pad;
-  if (rows > row_capacity) rows = row_capacity;
-  const int warps_per_block = blockDim.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int sub = lane & 7;
-  for (int64_t row = int64_t(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
-       row += int64_t(gridDim.x) * warps_per_block) {
-    const int n = __ldg(sorted_ids + row);
-    if (n < 0) continue;
-    const uint4* src_row = x + int64_t(n / topk) * groups_per_row * 16;
-    uint2* dst_row = xq + row * groups_per_row * 16;
-    for (int g0 = 0; g0 < groups_per_row; g0 += 4) {
-      const int g = g0 + (lane >> 3);
-      if (g < groups_per_row) {  // whole 8-lane groups take this branch together
-        const uint4* src = src_row + g * 16 + sub * 2;
-        uint32_t w[4];
-        const float scale = quantize_slice16(__ldg(src), __ldg(src + 1), w);
-        uint2* dst = dst_row + g * 16 + sub * 2;
-        dst[0] = make_uint2(w[0], w[1]);
-        dst[1] = make_uint2(w[2], w[3]);
-        if (sub == 0) scales_t[int64_t(g) * row_capacity + row] = scale;
-      }
-    }
-  }
-}
-
 int grid_for(int64_t work_items, int threads, int device_sms, int waves) {
   int64_t blocks = (work_items + threads - 1) / threads;
   int64_t cap = int64_t(device_sms) * waves;
@@ -140,14 +103,9 @@ int grid_for(int64_t work_items, int threads, int device_sms, int waves) {
 }
 
 int sm_count() {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      sms = 148;
-  }
-  return sms;
+  int dev = 0;
+  const int sms = cudaGetDevice(&dev) == cudaSuccess ? device_sm_count(dev) : 0;
+  return sms > 0 ? sms : 148;
 }
 
 }  // namespace
@@ -173,19 +131,6 @@ int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uin
   group_quant_fp8_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(x), rows,
                                                         hidden / 128, reinterpret_cast<uint2*>(q), scales,
                                                         scale_ld, transposed);
-  MB200_CHECK_CUDA(cudaGetLastError());
-  return kOk;
-}
-
-int launch_gather_quant_fp8(const __nv_bfloat16* x, const Schedule& sched, int local_experts, int topk,
-                            int hidden, uint8_t* xq, float* scales_t, int64_t row_capacity,
-                            cudaStream_t stream) {
-  MB200_REQUIRE(hidden % 128 == 0, kUnsupportedShape, "gather_quant: hidden=%d must be a multiple of 128", hidden);
-  const int threads = 256;
-  const int blocks = grid_for(row_capacity * 32, threads, sm_count(), 16);
-  gather_quant_fp8_kernel<<<blocks, threads, 0, stream>>>(
-      reinterpret_cast<const uint4*>(x), sched.sorted_ids, sched.mtile_prefix, local_experts, topk,
-      hidden / 128, reinterpret_cast<uint2*>(xq), scales_t, row_capacity, sched.pad_rows);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -71,22 +71,3 @@ def test_plugin_refuses_cpu_tensors():
         impl.setup(prob)
     with pytest.raises(ValueError):
         get_implementation("nope")
-
-
-def test_diagnostics_artefacts_build_and_bind():
-    """The probe build exports the same ABI; the diagnostics module parses its
-    command line and refuses to run without a GPU."""
-    import os
-
-    from moe_bench_b200 import build as B
-    from moe_bench_b200 import diagnostics as D
-
-    probe, tool = B.build_diagnostics()
-    assert os.path.exists(probe) and os.access(tool, os.X_OK)
-    lib = capi.load_library(probe)
-    assert lib.mb200_abi_version() == capi.ABI_VERSION
-    import torch
-
-    if not torch.cuda.is_available():
-        with pytest.raises(SystemExit, match="CUDA device"):
-            D.main(["mma-rate"])

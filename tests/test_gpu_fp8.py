@@ -63,7 +63,7 @@ def test_fp8_gemm_stages(tokens, hidden, inter, experts, topk, dist, cols):
     a[rows] = xq.view(torch.uint8)[row_tok]
     a_s_t = torch.ones(hidden // 128, cap)
     a_s_t[:, rows] = xs[row_tok].t()
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(64, dtype=torch.int32, device=DEV)
     actq = torch.zeros(cap, inter, dtype=torch.uint8, device=DEV)
     acts_t = torch.zeros(inter // 128, cap, dtype=torch.float32, device=DEV)
     capi.grouped_gemm_fp8(
@@ -71,7 +71,7 @@ def test_fp8_gemm_stages(tokens, hidden, inter, experts, topk, dist, cols):
         counts, prefix, sorted_ids, None, actq, acts_t, status, cols=cols,
     )
     torch.cuda.synchronize()
-    assert int(status.item()) == 0
+    assert int(status[0].item()) == 0
     # oracle: block matmul -> SiLU-mul -> bf16 -> group quant
     ref_act = torch.zeros(len(rows), inter)
     for e in range(experts):
@@ -97,7 +97,7 @@ def test_fp8_gemm_stages(tokens, hidden, inter, experts, topk, dist, cols):
         sorted_ids, w.to(DEV), y, None, status, cols=cols,
     )
     torch.cuda.synchronize()
-    assert int(status.item()) == 0
+    assert int(status[0].item()) == 0
     ref_y = torch.zeros(len(rows), hidden)
     aq_rows = actq.cpu()[rows].view(torch.float8_e4m3fn)
     for e in range(experts):

@@ -175,44 +175,3 @@ def test_dsv32_full_size_properties(dsv32, tokens):
     _, small = _run(sub)
     res = O.verify_output("bf16", small, big[idx].float(), atol=4e-3)
     assert res.passed and res.rel_err < 1e-3, (res.message, res.rel_err)
-
-
-_PAIR_CHILD = r"""
-import sys, torch
-sys.path.insert(0, sys.argv[1])
-from moe_bench_b200 import problem as P
-from moe_bench_b200.plugin import get_implementation
-outs = {}
-for tokens, hidden, inter, experts, topk in ((700, 512, 384, 4, 2), (33, 256, 128, 8, 2)):
-    cfg = P.MoEBenchConfig(hidden_size=hidden, intermediate_size=inter, num_experts=experts, topk=topk,
-                           world_size=1, seed=11, device="cuda:0")
-    prob = P.make_problem(cfg, tokens)
-    impl = get_implementation("b200"); impl.setup(prob)
-    out = impl.run(prob); assert impl.device_status() == 0
-    outs[f"{tokens}"] = out.cpu()
-torch.save(outs, sys.argv[2])
-"""
-
-
-def test_cta_pair_kernel_is_bit_identical(tmp_path):
-    """The opt-in CTA-pair (cta_group::2) variant of the 16-bit GEMMs computes the
-    same sums in the same order: its outputs equal the single-CTA kernel's bit for
-    bit.  The variant is chosen once per process from MB200_PAIR_MIN_ROWS, so each
-    mode runs in a child process.  intermediate 384 = 3 feature blocks: the second
-    CTA of the last pair has no feature block of its own."""
-    import os
-    import subprocess
-    import sys
-
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    got = {}
-    for mode, rows in (("single", "0"), ("pair", "1")):
-        path = str(tmp_path / f"{mode}.pt")
-        env = dict(os.environ, MB200_PAIR_MIN_ROWS=rows)
-        r = subprocess.run([sys.executable, "-c", _PAIR_CHILD, root, path], env=env, capture_output=True,
-                           text=True, timeout=240)
-        assert r.returncode == 0, r.stderr[-2000:]
-        got[mode] = torch.load(path)
-    for key in got["single"]:
-        assert torch.equal(got["single"][key], got["pair"][key]), key
-        assert bool(got["single"][key].float().abs().sum() > 0)
