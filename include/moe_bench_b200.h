@@ -142,6 +142,21 @@ int mb200_grouped_gemm_bf16_gated(const void* a, int64_t row_capacity, const voi
 int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int intermediate,
                               int local_experts, int topk);
 
+/* Where the forward entry points keep their intermediate tables inside the
+ * workspace, for checks that read them back (the reference validates its
+ * dispatch by comparing the gathered rows with x[src] byte for byte,
+ * tools/validate_push3.py:90-95).  `tokens` is the number of token rows the
+ * call sorts (mb200_dist_forward: tokens * world); expected_rows = the
+ * assignments expected on this rank (tokens*topk, or that divided by world for
+ * expert parallel), which picks the fp8 kernel family and its padding.
+ * out10 = { pad_rows, row_capacity, then byte offsets of: counts[E],
+ * mtile_prefix[E+1], sorted_ids[row_capacity], inverse[tokens*topk], the sorted
+ * row buffer [row_capacity][hidden] (16-bit or e4m3), its scales
+ * [hidden/128][row_capacity] (fp8, else 0), act [row_capacity][intermediate],
+ * y [tokens*topk][hidden] }. */
+int mb200_forward_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts,
+                         int topk, int64_t expected_rows, int64_t* out10);
+
 /* The layer forward, bf16 (reference.py:98-116 + 170-182; baseline.py:62-76):
  * out[t, :] = sum_j topk_weights[t, j] * ( SiLU(x_t.w1g[e]) * (x_t.w1u[e]) ) . w2[e],
  * e = expert_map[topk_ids[t, j]], skipping experts that are not local.

@@ -44,6 +44,7 @@ SIGNATURES = {
         [c_vp, c_i64, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_vp],
     ),
     "mb200_workspace_bytes": (c_i64, [c_i32, c_i64, c_i32, c_i32, c_i32, c_i32]),
+    "mb200_forward_layout": (c_i32, [c_i32, c_i64, c_i32, c_i32, c_i32, c_i32, c_i64, c_vp]),
     "mb200_moe_forward_bf16": (
         c_i32,
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i64, c_i32, c_vp],
@@ -152,6 +153,19 @@ def workspace_bytes(precision: int, tokens: int, hidden: int, intermediate: int,
     if n < 0:
         raise MB200Error(f"workspace_bytes: {load().mb200_last_error().decode()}")
     return n
+
+
+LAYOUT_FIELDS = ("pad_rows", "row_capacity", "counts", "mtile_prefix", "sorted_ids", "inverse", "rows", "row_scales",
+                 "act", "y")
+
+
+def forward_layout(precision: int, tokens: int, hidden: int, intermediate: int, local_experts: int, topk: int,
+                   expected_rows: int) -> dict:
+    """Padding, row capacity and the byte offsets of the forward's tables inside its workspace."""
+    out = (ctypes.c_int64 * 10)()
+    _check(load().mb200_forward_layout(precision, tokens, hidden, intermediate, local_experts, topk, expected_rows,
+                                       out), "forward_layout")
+    return dict(zip(LAYOUT_FIELDS, [int(v) for v in out]))
 
 
 def route_topk(logits: torch.Tensor, topk: int):

@@ -347,6 +347,24 @@ int64_t mb200_workspace_bytes(int precision, int64_t tokens, int hidden, int int
   return make_layout(precision, tokens, hidden, intermediate, local_experts, topk, pad_rows_of(precision)).total;
 }
 
+int mb200_forward_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk,
+                         int64_t expected_rows, int64_t* out10) {
+  MB200_REQUIRE(out10 != nullptr, kInvalidArgument, "forward_layout: null pointer");
+  MB200_REQUIRE(precision == MB200_PRECISION_BF16 || precision == MB200_PRECISION_FP8 ||
+                    precision == MB200_PRECISION_FP16,
+                kInvalidArgument, "forward_layout: unknown precision %d", precision);
+  int rc = check_shape(tokens, hidden, intermediate, local_experts, topk);
+  if (rc) return rc;
+  const bool fp8 = precision == MB200_PRECISION_FP8;
+  if (fp8 && (rc = check_shape_fp8(hidden, intermediate))) return rc;
+  const int pad = fp8 ? fp8_pad_rows(expected_rows, local_experts) : kPadBf16;
+  const Layout l = make_layout(precision, tokens, hidden, intermediate, local_experts, topk, pad);
+  const int64_t v[10] = {pad, row_capacity(tokens, topk, local_experts, pad), l.counts, l.prefix, l.sorted,
+                         l.inverse, l.xg, l.xs, l.act, l.y};
+  for (int i = 0; i < 10; ++i) out10[i] = v[i];
+  return kOk;
+}
+
 static int moe_forward_16bit(int fp16, const void* hidden_states, const void* w1, const void* w2,
                              const int32_t* topk_ids, const float* topk_weights,
                              const int32_t* expert_map, void* out, int64_t tokens, int hidden,

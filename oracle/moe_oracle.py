@@ -133,15 +133,19 @@ def block_matmul(a_q, b_q, a_s, b_s, block_shape):
     and added in ascending k-block order (reference.py:65-95)."""
     bn, bk = block_shape
     a = a_q.float()
-    b = b_q.float()
+    b = b_q.float()  # converted where it lives (a GPU tensor is converted there), multiplied on the CPU
+    a, b = a.cpu(), b.cpu()
+    a_s, b_s = a_s.float().cpu(), b_s.float().cpu()
     m, k = a.shape
     n = b.shape[0]
     out = torch.zeros(m, n, dtype=torch.float32)
+    # scale of every output column for k-block i: b_s[j, i] of the column's n-block j
+    col_block = torch.arange(n) // bn
     for i in range(-(-k // bk)):
         ks = slice(i * bk, min((i + 1) * bk, k))
-        for j in range(-(-n // bn)):
-            ns = slice(j * bn, min((j + 1) * bn, n))
-            out[:, ns] += (a[:, ks] @ b[ns, ks].t()) * (a_s[:, i : i + 1] * b_s[j, i])
+        # all n-blocks of this k-block in one product; each element still receives
+        # (partial * (a_s * b_s)) added in ascending k-block order, as in the reference's loop
+        out += (a[:, ks] @ b[:, ks].t()) * (a_s[:, i : i + 1] * b_s[col_block, i].unsqueeze(0))
     return out
 
 
@@ -170,8 +174,9 @@ def moe_dense(hidden_states, w1, w2, topk_ids, expert_map):
         if sel.numel() == 0:
             continue
         # weights may live on another device: only touched experts are copied
-        h = x[tok[sel]] @ w1[e].cpu().float().t()
-        out[sel] = silu_and_mul(h) @ w2[e].cpu().float().t()
+        # (converted to fp32 where they live, multiplied on the CPU)
+        h = x[tok[sel]] @ w1[e].float().cpu().t()
+        out[sel] = silu_and_mul(h) @ w2[e].float().cpu().t()
     return out.view(t, topk, k_dim)
 
 
@@ -189,10 +194,10 @@ def moe_fp8(hidden_states, w1, w2, w1_scale, w2_scale, topk_ids, expert_map, blo
         sel = (slots == e).nonzero().flatten()
         if sel.numel() == 0:
             continue
-        h = block_matmul(xq[tok[sel]], w1[e].cpu(), xs[tok[sel]], w1_scale[e].cpu(), block_shape)
+        h = block_matmul(xq[tok[sel]], w1[e], xs[tok[sel]], w1_scale[e], block_shape)
         act = silu_and_mul(h).to(base_dtype)
         aq, a_s = group_quant_fp8(act, block_shape[1])
-        out[sel] = block_matmul(aq, w2[e].cpu(), a_s, w2_scale[e].cpu(), block_shape)
+        out[sel] = block_matmul(aq, w2[e], a_s, w2_scale[e], block_shape)
     return out.view(t, topk, k_dim)
 
 
