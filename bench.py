@@ -170,31 +170,70 @@ def _cpu_sample_problem(tokens: int):
     return prob
 
 
+def _staged_reference():
+    """The reference's own harness modules, if the build staged them next to the oracle
+    (they import vLLM, so this is slow the first time); None when they are not there or do
+    not import on this box."""
+    from oracle.stage_reference import staged_parent
+
+    parent = staged_parent()
+    if parent is None:
+        return None
+    os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+    if parent not in sys.path:
+        sys.path.insert(0, parent)
+    try:
+        import moe_bench.config as rc
+        import moe_bench.data as rd
+        import moe_bench.reference as rr
+    except Exception:  # noqa: BLE001
+        return None
+    return rc, rd, rr
+
+
 def _time_cpu_oracle(tokens: int, steps: int, warmup: int, budget_s: float = 25.0):
+    """The reference's CPU forward on a bounded sample, all host cores: the reference's own
+    ``reference_moe`` on its own generator's problem when its modules are staged
+    (kind "reference"), else the oracle port on the package's byte-identical problem (kind "port")."""
     import torch
 
     from oracle import moe_oracle as O
 
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    prob = _cpu_sample_problem(tokens)
+    ref = _staged_reference()
+    if ref is not None:
+        rc, rd, rr = ref
+        cfg = rc.MoEBenchConfig(
+            hidden_size=HIDDEN, intermediate_size=INTER, num_experts=EXPERTS, topk=TOPK,
+            parallel_mode=rc.ParallelMode.EP, world_size=64, precision=rc.Precision.BF16,
+            routing=rc.RoutingConfig(distribution=rc.Distribution.UNIFORM), seed=0, device="cpu",
+        )
+        prob = rd.make_problem(cfg, tokens, rank=0)
+        forward, kind = (lambda: rr.reference_moe(prob)), "reference"
+        what = "the reference's own reference_moe on its own generator's problem"
+    else:
+        prob = _cpu_sample_problem(tokens)
+        forward, kind = (lambda: O.reference_moe(prob)), "port"
+        what = "the oracle port, weights pre-converted to fp32"
     assignments = prob.num_local_assignments
     flops = 6.0 * INTER * HIDDEN * assignments
     for _ in range(warmup):
-        O.reference_moe(prob)
+        forward()
     times = []
     t_begin = time.perf_counter()
     for _ in range(steps):
         t0 = time.perf_counter()
-        O.reference_moe(prob)
+        forward()
         times.append(time.perf_counter() - t0)
         if time.perf_counter() - t_begin > budget_s:
             break
     avg = sum(times) / len(times)
     return {
-        "value": flops / avg / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+        "value": flops / avg / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
         "sample": f"experts 0-3 of 256 with all {assignments} assignments of a {tokens}-token batch "
-                  f"(DSv3.2 dims, weights pre-converted to fp32), {len(times)} passes, {avg * 1e3:.1f} ms each",
+                  f"(DSv3.2 dims; {what}), {len(times)} passes, {avg * 1e3:.1f} ms each; the sample is one "
+                  "host's work and does not grow with the GPU count",
         "ms_per_pass": avg * 1e3, "passes": len(times),
     }
 
