@@ -157,7 +157,7 @@ int check_shape(int64_t tokens, int hidden, int intermediate, int local_experts,
 int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int local_experts, int hidden,
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
-                   unsigned long long* clock_probe, const FusedDispatch* dispatch, int fp16) {
+                   unsigned long long* clock_probe, const FusedDispatch* dispatch, int fp16, const FusedPush* push) {
   CUtensorMap map_w;
   TokenMaps maps_t;
   GemmArgs g{};
@@ -190,7 +190,9 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
     g.out_cols = hidden;
   }
   FusedDispatch none{};
-  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, dispatch ? *dispatch : none, device, stream);
+  FusedPush no_push{};
+  return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, dispatch ? *dispatch : none,
+                                  push ? *push : no_push, device, stream);
 }
 
 int check_shape_fp8(int hidden, int intermediate) {
@@ -204,7 +206,8 @@ int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t 
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,
                        void* out, float* out_scale_t, int* status, int device, cudaStream_t stream,
-                       unsigned long long* clock_probe, int pad_rows) {
+                       unsigned long long* clock_probe, int pad_rows, const FusedDispatchFp8* dispatch,
+                       const FusedPush* push) {
   CUtensorMap map_a, map_b;
   GemmFp8Args g{};
   g.clock_probe = clock_probe;
@@ -250,8 +253,13 @@ int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t 
     g.scale_rows_per_expert = hidden / 128;
     g.scale_half_offset = 0;
   }
+  MB200_REQUIRE(!cols || (!dispatch && !push), kInvalidArgument,
+                "fp8: fused dispatch / push exist only in the 128-row-tile kernel");
   if (cols) return launch_grouped_gemm_fp8_cols(GemmMode(mode), map_b, maps_t, g, device, stream);
-  return launch_grouped_gemm_fp8(GemmMode(mode), map_a, map_b, g, device, stream);
+  const FusedDispatchFp8 no_disp{};
+  const FusedPush no_push{};
+  return launch_grouped_gemm_fp8(GemmMode(mode), map_a, map_b, g, dispatch ? *dispatch : no_disp,
+                                 push ? *push : no_push, device, stream);
 }
 
 }  // namespace mb200

@@ -192,6 +192,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
       : "memory");
 }
 
+// Untiled bulk copy global -> shared (this CTA), completion on an mbarrier.  Both
+// addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
 // ---- tcgen05 / tensor memory ----------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),

@@ -109,6 +109,7 @@ struct TileCoord {
   int row0;     // first sorted row of the token block
   int ntok;     // token columns computed (multiple of 16)
   int valid;    // real tokens among them
+  int tb;       // index of the token block among all token blocks of the schedule
 };
 
 // Tiles are numbered expert-major; inside an expert the token blocks of one
@@ -133,6 +134,7 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, const SmemTail* t, co
   int len16 = blocks16 - start16;
   if (len16 > per) len16 = per;
   c.row0 = (t->prefix[lo] + start16) * kPad;
+  c.tb = t->tb_prefix[lo] + j;
   c.ntok = len16 * kPad;
   int left = __ldg(counts + lo) - start16 * kPad;
   c.valid = left < 0 ? 0 : (left < c.ntok ? left : c.ntok);
@@ -153,11 +155,13 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-template <int kMode>
+// kPush (down GEMM, expert parallel): warps 10-13 forward finished rows to the GPUs that own
+// the tokens instead of draining accumulators.
+template <int kMode, bool kPush>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ TokenMaps maps_t, const GemmArgs args,
-                         const FusedDispatch disp) {
+                         const FusedDispatch disp, const FusedPush push) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -169,7 +173,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
   const int lane = threadIdx.x & 31;
   const int E = args.num_experts;
   // the down GEMM has no dispatch: its warps 10-13 drain accumulators too
-  constexpr int kEpiWarps = kMode == kDownWeighted ? kEpilogueWarps + kDispatchWarps : kEpilogueWarps;
+  constexpr int kEpiWarps = (kMode == kDownWeighted && !kPush) ? kEpilogueWarps + kDispatchWarps : kEpilogueWarps;
   constexpr int kChunkStride = kEpiWarps / 4;  // warps per tensor-memory lane quarter
   const int worker = int(blockIdx.x);
   const int workers = int(gridDim.x);
@@ -389,6 +393,69 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
         if (lane == 0) atomicAdd(disp.granule_done + g, 1);
       }
     }
+  } else if (kMode == kDownWeighted && kPush && warp >= kFirstDispatchWarp) {
+    // ---------------- fused combine push (down GEMM, expert parallel) ----------------
+    // Work unit = one 16-row granule of the sorted rows, granules strided over the CTAs in row
+    // order (= the order in which the tiles finish).  A granule is forwarded once every feature
+    // block of its token block has been stored by the epilogue warps of whichever CTAs computed
+    // them.  The GEMM warps never wait for these warps, so with all CTAs resident (cooperative
+    // launch) the wait cannot deadlock; it is bounded like every other wait.
+    const int pw = warp - kFirstDispatchWarp;
+    const int granules = tail->prefix[E];
+    const int target = args.n_tiles * kEpiWarps;
+    bool ok = true;
+    for (int g = blockIdx.x; ok && g < granules; g += gridDim.x) {
+      int lo = 0, hi = E - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (tail->prefix[mid] <= g) lo = mid; else hi = mid - 1;
+      }
+      const int blocks16 = tail->prefix[lo + 1] - tail->prefix[lo];
+      const int nb = tail->tb_prefix[lo + 1] - tail->tb_prefix[lo];
+      const int per = (blocks16 + nb - 1) / nb;
+      const int tb = tail->tb_prefix[lo] + (g - tail->prefix[lo]) / per;
+      uint32_t spins = 0;
+      WaitClock clock;
+      while (true) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(push.block_done + tb) : "memory");
+        if (v >= target) break;
+        if ((++spins & 0x3F) == 0) {
+          const bool aborted = __any_sync(0xffffffffu, *ctx.abort_flag != 0);
+          const bool late = __any_sync(0xffffffffu, clock.expired(ctx));
+          if (aborted || late) {
+            if (!aborted && lane == 0) wait_give_up(ctx, 7);
+            ok = false;
+            break;
+          }
+        }
+        __nanosleep(256);
+      }
+      if (!ok) break;
+      for (int i = pw; i < kPad; i += kDispatchWarps) {
+        const int n = __ldg(args.sorted_ids + g * kPad + i);
+        if (n >= push.own_rows) {  // a token of another rank (own tokens were stored in place; -1 = padding)
+          const int tok_global = n / push.topk;
+          const int ring = tok_global / push.tokens_per_rank;
+          const int slot = n - ring * push.own_rows;
+          const uint4* src = push.rows_in + size_t(n) * push.vec_per_row;
+          uint4* dst = reinterpret_cast<uint4*>(push.dst.ptr[(push.rank + ring) % push.world]) +
+                       size_t(slot) * push.vec_per_row;
+          for (int v0 = lane; v0 < push.vec_per_row; v0 += 32 * kDispatchLoads) {
+            uint4 buf[kDispatchLoads];
+#pragma unroll
+            for (int u = 0; u < kDispatchLoads; ++u)
+              if (v0 + u * 32 < push.vec_per_row) buf[u] = __ldcg(src + v0 + u * 32);
+#pragma unroll
+            for (int u = 0; u < kDispatchLoads; ++u)
+              if (v0 + u * 32 < push.vec_per_row) dst[v0 + u * 32] = buf[u];
+          }
+        }
+      }
+    }
+    // this warp's stores to the peers are performed before the kernel ends (the cross-GPU
+    // barrier that follows on the stream then covers them)
+    __threadfence_system();
   } else {
     // ---------------- epilogue: 8 (gate/up) or 12 (down) warps, one accumulator row (feature) per thread ----------------
     const int ew = warp - kFirstEpilogueWarp;
@@ -425,6 +492,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       const uint32_t t0 = tmem_base + buf * 256 + (uint32_t(quarter * 32) << 16);
       const uint32_t t1 = t0 + acc1_off;
       uint16_t* out = reinterpret_cast<uint16_t*>(args.out);
+      uint16_t* out_own = kPush ? reinterpret_cast<uint16_t*>(push.dst.ptr[push.rank]) : out;
       const int chunks = tc.ntok >> 4;
 
       // A thread holds one feature (accumulator row) of 16 tokens; memory wants the
@@ -492,9 +560,12 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
               const int piece = lane + 32 * h;
               const int a = tail->tile_assign[par][c * 16 + (piece >> 2)];
               const int feat = feat_base + half * 128 + (piece & 3) * 8;
-              if (a >= 0 && feat < args.out_cols)
-                *reinterpret_cast<uint4*>(out + size_t(a) * args.out_cols + feat) =
+              if (a >= 0 && feat < args.out_cols) {
+                // expert parallel: rows of this rank's own tokens go straight into its receive buffer
+                uint16_t* base = (kPush && a < push.own_rows) ? out_own : out;
+                *reinterpret_cast<uint4*>(base + size_t(a) * args.out_cols + feat) =
                     *reinterpret_cast<const uint4*>(sc0 + piece * 8);
+              }
             }
             __syncwarp();
           }
@@ -516,6 +587,12 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
         }
       }
       if (!released) release();
+      if (kPush) {
+        // this warp's share of the token block is stored: count it for the push warps
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(push.block_done + tc.tb, 1);
+      }
     }
   }
 
@@ -538,38 +615,44 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 }
 
-using KernelFn = void (*)(const CUtensorMap, const TokenMaps, const GemmArgs, const FusedDispatch);
+using KernelFn = void (*)(const CUtensorMap, const TokenMaps, const GemmArgs, const FusedDispatch, const FusedPush);
 
 }  // namespace
 
 int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
-                             const GemmArgs& args, const FusedDispatch& dispatch, int device,
-                             cudaStream_t stream) {
+                             const GemmArgs& args, const FusedDispatch& dispatch, const FusedPush& push,
+                             int device, cudaStream_t stream) {
   MB200_REQUIRE(args.num_experts >= 1 && args.num_experts <= kMaxExperts, kUnsupportedShape,
                 "grouped_gemm: %d local experts, supported 1..%d", args.num_experts, kMaxExperts);
   MB200_REQUIRE(!dispatch.enabled || mode == kGateUpSwiglu, kInvalidArgument,
                 "grouped_gemm: fused dispatch belongs to the gate/up stage");
   MB200_REQUIRE((reinterpret_cast<uintptr_t>(args.out) & 15) == 0 && args.out_cols % 8 == 0, kInvalidArgument,
                 "grouped_gemm: output must be 16-byte aligned with a row length that is a multiple of 8");
-  KernelFn kernel = mode == kGateUpSwiglu ? grouped_gemm_bf16_kernel<kGateUpSwiglu>
-                                          : grouped_gemm_bf16_kernel<kDownWeighted>;
+  MB200_REQUIRE(!push.enabled || mode == kDownWeighted, kInvalidArgument,
+                "grouped_gemm: the fused combine push belongs to the down stage");
+  const int variant = mode == kGateUpSwiglu ? 0 : (push.enabled ? 2 : 1);
+  KernelFn kernel = variant == 0   ? grouped_gemm_bf16_kernel<kGateUpSwiglu, false>
+                    : variant == 1 ? grouped_gemm_bf16_kernel<kDownWeighted, false>
+                                   : grouped_gemm_bf16_kernel<kDownWeighted, true>;
   // once per device and kernel; a second thread that sets it again does no harm
-  static std::atomic<bool> configured[kMaxDevices][2];
-  if (device < 0 || device >= kMaxDevices || !configured[device][mode].load(std::memory_order_acquire)) {
+  static std::atomic<bool> configured[kMaxDevices][3];
+  if (device < 0 || device >= kMaxDevices || !configured[device][variant].load(std::memory_order_acquire)) {
     MB200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
-    if (device >= 0 && device < kMaxDevices) configured[device][mode].store(true, std::memory_order_release);
+    if (device >= 0 && device < kMaxDevices) configured[device][variant].store(true, std::memory_order_release);
   }
   const int sms = device_sm_count(device);
   MB200_REQUIRE(sms > 0, kCudaError, "grouped_gemm: cannot read the SM count of device %d", device);
-  if (dispatch.enabled == kDispatchFused) {
-    // the tile loader waits for rows that other CTAs' dispatch warps deliver: all
-    // CTAs must be resident, which a cooperative launch guarantees (or refuses)
+  if (dispatch.enabled == kDispatchFused || push.enabled) {
+    // the tile loader waits for rows that other CTAs' dispatch warps deliver, the push warps
+    // for tiles that other CTAs compute: all CTAs must be resident, which a cooperative
+    // launch guarantees (or refuses)
     void* params[] = {const_cast<CUtensorMap*>(&map_w), const_cast<TokenMaps*>(&maps_t),
-                      const_cast<GemmArgs*>(&args), const_cast<FusedDispatch*>(&dispatch)};
+                      const_cast<GemmArgs*>(&args), const_cast<FusedDispatch*>(&dispatch),
+                      const_cast<FusedPush*>(&push)};
     MB200_CHECK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(sms), dim3(kThreads),
                                                  params, kSmemBytes, stream));
   } else {
-    kernel<<<sms, kThreads, kSmemBytes, stream>>>(map_w, maps_t, args, dispatch);
+    kernel<<<sms, kThreads, kSmemBytes, stream>>>(map_w, maps_t, args, dispatch, push);
     MB200_CHECK_CUDA(cudaGetLastError());
   }
   return kOk;

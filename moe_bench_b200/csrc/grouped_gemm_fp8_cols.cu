@@ -46,6 +46,7 @@ constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
 constexpr int kMaxTokens = 128;           // columns per accumulator (two partial pairs fit tensor memory)
 constexpr int kMaxKBlocks = 128;
 constexpr int kMaxPartials = 16;          // partial accumulator pairs in flight (16-token box)
+constexpr int kScaleFloats = 1024;        // activation scales of the K blocks in flight (see SmemTail::ascale)
 
 struct SmemTail {
   uint64_t full[kMaxStages];
@@ -57,6 +58,11 @@ struct SmemTail {
   int abort_flag;
   int max_blocks16;
   float wscale[2][2][kMaxKBlocks];      // [tile parity][accumulator][k block]
+  // Activation scales of the K blocks in flight: slots of tb_rows floats, filled by the TMA warp
+  // together with the stage (a load issued by the epilogue threads themselves would wait
+  // microseconds behind the weight stream).  A slot is reused after stages + partials + 1 K
+  // blocks at the earliest, and kScaleFloats / tb_rows slots are always more than that.
+  alignas(16) float ascale[kScaleFloats];
   float col_amax[2][4][kMaxTokens];     // [tile parity][lane quarter][token column]
   int tile_assign[2][kMaxTokens];
   float tile_weight[2][kMaxTokens];
@@ -71,6 +77,7 @@ constexpr size_t kSmemBytes = 1024 + kRingBytes + sizeof(SmemTail);
 struct Geometry {
   int box_index, tb_rows, stage_bytes, stages;
   int partials;  // partial accumulator pairs that fit the 512 tensor-memory columns
+  int scale_slots;
 };
 
 __device__ __forceinline__ Geometry make_geometry(int max_blocks16) {
@@ -82,6 +89,7 @@ __device__ __forceinline__ Geometry make_geometry(int max_blocks16) {
   const int s = int(kRingBytes) / g.stage_bytes;
   g.stages = s > kMaxStages ? kMaxStages : s;
   g.partials = kTmemCols / (2 * g.tb_rows);
+  g.scale_slots = kScaleFloats / g.tb_rows;  // 8 / 16 / 32 / 64 slots >= stages + partials + 1 for every box
   return g;
 }
 
@@ -218,6 +226,7 @@ grouped_gemm_fp8_cols_kernel(const __grid_constant__ CUtensorMap map_w,
     if (lane == 0) prefetch_tmap(map_t);
     int stage = 0;
     uint32_t phase = 0;
+    int slot = 0;  // scale slot of the K block being loaded
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const TileCoord tc = decode_tile(tile, tail, args.counts, E, args.n_tiles);
@@ -230,7 +239,9 @@ grouped_gemm_fp8_cols_kernel(const __grid_constant__ CUtensorMap map_w,
           const uint32_t w_dst = ring_addr + stage * geo.stage_bytes;
           const uint32_t t_dst = w_dst + kWeightBytes;
           const int kcol = kb * 128;
-          mbar_expect_tx(bar, uint32_t(geo.stage_bytes));
+          mbar_expect_tx(bar, uint32_t(geo.stage_bytes + tc.ntok * 4));
+          tma_load_1d(smem_u32(tail->ascale + slot * geo.tb_rows),
+                      args.a_scale_t + size_t(kb) * args.row_capacity + tc.row0, uint32_t(tc.ntok * 4), bar);
           if (kMode == kGateUpSwiglu) {
             tma_load_2d(w_dst, &map_w, kcol, w_row + tc.fblock * 128, bar);
             tma_load_2d(w_dst + kWeightBytes / 2, &map_w, kcol,
@@ -242,6 +253,7 @@ grouped_gemm_fp8_cols_kernel(const __grid_constant__ CUtensorMap map_w,
         }
         __syncwarp();
         if (++stage == geo.stages) { stage = 0; phase ^= 1; }
+        if (++slot == geo.scale_slots) slot = 0;
       }
     }
   } else if (warp == 1) {
@@ -287,51 +299,55 @@ grouped_gemm_fp8_cols_kernel(const __grid_constant__ CUtensorMap map_w,
     const int r = quarter * 32 + lane;
     const int etid = threadIdx.x - kFirstEpilogueWarp * 32;
     uint32_t pbuf = 0, puse = 0, it = 0, epi_phase = 0;
+    int slot = 0;  // scale slot of the K block being folded in
     bool ok = true;
+    // Per-tile tables: weight scales of the two accumulators (thread i fetches element i of
+    // [accumulator][kb]); down GEMM: destination row and combine weight of token column i.
+    // They are fetched for tile t+1 while tile t is computed, so their latency never shows.
+    struct TileTables { float ws; int assign; float weight; };
+    auto fetch_tables = [&](int tile) -> TileTables {
+      TileTables t{0.f, -1, 0.f};
+      if (tile >= total_tiles) return t;
+      const TileCoord nt = decode_tile(tile, tail, args.counts, E, args.n_tiles);
+      if (etid < 2 * k_blocks) {
+        const int h = etid / k_blocks, kb = etid - h * k_blocks;
+        const int sblock = (kMode == kGateUpSwiglu) ? (h * args.scale_half_offset + nt.fblock) : (2 * nt.fblock + h);
+        if (sblock < args.scale_rows_per_expert)
+          t.ws = __ldg(args.w_scale + (size_t(nt.expert) * args.scale_rows_per_expert + sblock) * k_blocks + kb);
+      }
+      if (kMode == kDownWeighted && etid < nt.valid) {
+        t.assign = __ldg(args.sorted_ids + nt.row0 + etid);
+        if (t.assign >= 0) t.weight = __ldg(args.row_scale + t.assign);
+      }
+      return t;
+    };
+    TileTables next = fetch_tables(blockIdx.x);
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
       const TileCoord tc = decode_tile(tile, tail, args.counts, E, args.n_tiles);
       const int par = it & 1;
-      // per-tile tables: weight scales of the two accumulators; down GEMM: destination rows
-      for (int i = etid; i < 2 * k_blocks; i += kEpilogueWarps * 32) {
-        const int h = i / k_blocks, kb = i - h * k_blocks;
-        const int sblock = (kMode == kGateUpSwiglu) ? (h * args.scale_half_offset + tc.fblock)
-                                                    : (2 * tc.fblock + h);
-        float v = 0.f;
-        if (sblock < args.scale_rows_per_expert)
-          v = __ldg(args.w_scale + (size_t(tc.expert) * args.scale_rows_per_expert + sblock) * k_blocks + kb);
-        tail->wscale[par][h][kb] = v;
-      }
-      if (kMode == kDownWeighted) {
-        for (int j = etid; j < tc.ntok; j += kEpilogueWarps * 32) {
-          int a = -1;
-          float w = 0.f;
-          if (j < tc.valid) {
-            a = __ldg(args.sorted_ids + tc.row0 + j);
-            if (a >= 0) w = __ldg(args.row_scale + a);
-          }
-          tail->tile_assign[par][j] = a;
-          tail->tile_weight[par][j] = w;
-        }
+      if (etid < 2 * k_blocks) (&tail->wscale[par][0][0])[(etid / k_blocks) * kMaxKBlocks + etid % k_blocks] = next.ws;
+      if (kMode == kDownWeighted && etid < kMaxTokens) {
+        tail->tile_assign[par][etid] = next.assign;
+        tail->tile_weight[par][etid] = next.weight;
       }
       ok = epilogue_barrier(&tail->epi_bar, epi_phase, ctx, lane);
       if (!ok) break;
+      next = fetch_tables(tile + int(gridDim.x));
 
       const int chunks = tc.ntok >> 4;                 // 16-column chunks in this tile (<= 8)
       const int my_chunks = (chunks - cgroup + 1) >> 1;  // chunks cgroup, cgroup+2, ... (<= 4)
       float acc0[64], acc1[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) { acc0[i] = 0.f; acc1[i] = 0.f; }
-      const float* a_scale = args.a_scale_t + tc.row0;  // [kb][row_capacity], this tile's columns
 
       for (int kb = 0; ok && kb < k_blocks; ++kb) {
-        // next K block's activation scales into L1 while this one is folded in
-        if (kb + 1 < k_blocks && lane < 4 && lane * 32 < tc.ntok)
-          asm volatile("prefetch.global.L1 [%0];" ::"l"(a_scale + size_t(kb + 1) * args.row_capacity + lane * 32));
         ok = mbar_wait(smem_u32(&tail->part_full[pbuf]), puse & 1, ctx, 4);
         if (!ok) break;
         tc_fence_after();
         const float w0 = tail->wscale[par][0][kb], w1 = tail->wscale[par][1][kb];
-        const float4* a_s4 = reinterpret_cast<const float4*>(a_scale + size_t(kb) * args.row_capacity);
+        // this K block's activation scales arrived in shared memory with its stage
+        const float4* a_s4 = reinterpret_cast<const float4*>(tail->ascale + slot * geo.tb_rows);
+        if (++slot == geo.scale_slots) slot = 0;
         const uint32_t t0 = tmem_base + pbuf * 2 * geo.tb_rows + (uint32_t(quarter * 32) << 16);
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -342,8 +358,8 @@ grouped_gemm_fp8_cols_kernel(const __grid_constant__ CUtensorMap map_w,
             tmem_ld16(t0 + geo.tb_rows + c * 16, p1);
             float as[16];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {  // the same 64 bytes for every lane: one L1 transaction
-              const float4 v = __ldg(a_s4 + c * 4 + q);
+            for (int q = 0; q < 4; ++q) {  // the same 16 bytes for every lane: a broadcast read
+              const float4 v = a_s4[c * 4 + q];
               as[4 * q] = v.x; as[4 * q + 1] = v.y; as[4 * q + 2] = v.z; as[4 * q + 3] = v.w;
             }
             tmem_ld_wait();
@@ -369,8 +385,11 @@ grouped_gemm_fp8_cols_kernel(const __grid_constant__ CUtensorMap map_w,
             const int c = cgroup + 2 * m;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float g = acc0[m * 16 + j];
-              const float v = bf16_round(g / (1.0f + __expf(-g)) * acc1[m * 16 + j]);
+              // columns beyond the expert's last token hold whatever the padding rows contained
+              // (possibly NaN or Inf, which would send the division down its slow path): zeroed
+              const bool col_ok = c * 16 + j < tc.valid;
+              const float g = col_ok ? acc0[m * 16 + j] : 0.f;
+              const float v = bf16_round(__fdividef(g, 1.0f + __expf(-g)) * (col_ok ? acc1[m * 16 + j] : 0.f));
               acc0[m * 16 + j] = v;
               float a = fabsf(v);
 #pragma unroll

@@ -84,6 +84,25 @@ struct FusedDispatch {
 // peer GPU's push); the kernel only waits for them.
 enum DispatchMode : int { kDispatchOff = 0, kDispatchFused = 1, kDispatchExternal = 2 };
 constexpr int kDispatchWarpsPerCta = 4;
+// Combine by push, fused into the down GEMM (expert parallel): the weighted rows of every
+// finished token block are forwarded by extra warps of the kernel to the GPU that owns the
+// token, straight into its receive buffer at the slot of the assignment (token*topk + kpos),
+// while later tiles compute.  Rows of this rank's own tokens are stored there by the epilogue
+// itself.  The owner then sums the k rows of each token (all of them arrive: every assignment
+// has exactly one expert rank).  Replaces the reduce-scatter of schemes.py:142; the shape of
+// the reference's push combine (kernels/tk/tk_moe.cu:1251-1519) without its pre-reduction.
+struct FusedPush {
+  PeerTable dst;          // [rank] -> receive buffer [tokens_per_rank*topk][hidden] 16-bit of that rank
+  int rank, world;        // flat assignment n = ((ring*T + t)*topk + j), owner = (rank + ring) mod world
+  int tokens_per_rank;
+  int topk;
+  int vec_per_row;        // hidden / 8 (16-byte vectors per row)
+  int own_rows;           // tokens_per_rank * topk: n < own_rows are this rank's own tokens
+  const uint4* rows_in;   // the down GEMM's local output [all assignments][hidden] the pushes read
+  int* block_done;        // [token blocks] epilogue-warp arrivals per token block, zeroed before the launch
+  int enabled;
+};
+
 // Token-operand tensor maps with boxes of 16, 32, 64, 128 and 256 rows; the
 // kernel picks one from the largest expert segment it finds in the schedule.
 constexpr int kTokenBoxes = 5;
@@ -91,8 +110,8 @@ struct TokenMaps {
   CUtensorMap m[kTokenBoxes];
 };
 int launch_grouped_gemm_bf16(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
-                             const GemmArgs& args, const FusedDispatch& dispatch, int device,
-                             cudaStream_t stream);
+                             const GemmArgs& args, const FusedDispatch& dispatch, const FusedPush& push,
+                             int device, cudaStream_t stream);
 
 // grouped_gemm_fp8.cu: e4m3 operands, fp32 block scales applied in the epilogue
 struct GemmFp8Args {
@@ -116,8 +135,25 @@ struct GemmFp8Args {
   int* status;
   unsigned long long* clock_probe;  // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel
 };
+// Dispatch fused into the fp8 gate/up GEMM (128-row-tile kernel): two helper warps of every CTA
+// fill the sorted row buffer with the tokens' e4m3 rows and their 1x128 scales, 16-row granule by
+// granule, from this GPU's quantised tokens or with P2P loads from the source ranks.
+struct FusedDispatchFp8 {
+  PeerTable xq;           // [rank] -> quantised tokens [tokens_per_rank][hidden] e4m3
+  PeerTable xs;           // [rank] -> their scales [tokens_per_rank][hidden/128] fp32
+  int rank, world;        // flat assignment n = ((ring*T + t)*topk + j), source = (rank + ring) mod world
+  int tokens_per_rank;
+  int topk;
+  int groups_per_row;     // hidden / 128
+  uint4* rows_out;        // sorted rows [row_capacity][hidden] e4m3
+  float* scales_t_out;    // [hidden/128][row_capacity]
+  int* granule_done;      // [row_capacity / 16] arrival counters, zeroed before the launch
+  int enabled;
+};
+constexpr int kFp8HelperWarps = 2;  // dispatch / push warps of the fp8 128-row-tile kernel
 int launch_grouped_gemm_fp8(GemmMode mode, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                            const GemmFp8Args& args, int device, cudaStream_t stream);
+                            const GemmFp8Args& args, const FusedDispatchFp8& dispatch, const FusedPush& push,
+                            int device, cudaStream_t stream);
 // grouped_gemm_fp8_cols.cu: same arithmetic, tokens on the accumulator columns (schedule padded to 16)
 int launch_grouped_gemm_fp8_cols(GemmMode mode, const CUtensorMap& map_w, const TokenMaps& maps_t,
                                  const GemmFp8Args& args, int device, cudaStream_t stream);
@@ -160,12 +196,13 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
                    int intermediate, const int* counts, const int* prefix, const int* sorted,
                    const float* row_scale, void* out, int* status, int device, cudaStream_t stream,
                    unsigned long long* clock_probe = nullptr, const FusedDispatch* dispatch = nullptr,
-                   int fp16 = 0);
+                   int fp16 = 0, const FusedPush* push = nullptr);
 int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t cap, const void* w,
                        const float* w_scale, int local_experts, int hidden, int intermediate,
                        const int* counts, const int* prefix, const int* sorted, const float* row_scale,
                        void* out, float* out_scale_t, int* status, int device, cudaStream_t stream,
-                       unsigned long long* clock_probe = nullptr, int pad_rows = kTileM);
+                       unsigned long long* clock_probe = nullptr, int pad_rows = kTileM,
+                       const FusedDispatchFp8* dispatch = nullptr, const FusedPush* push = nullptr);
 void mark_stage(int i, cudaStream_t s);
 
 // ---- tensormap.cu ----------------------------------------------------------------------
