@@ -128,8 +128,13 @@ Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, 
   l.act = take(cap * intermediate * eb);
   l.y = take((a > 0 ? a : 1) * int64_t(hidden) * 2);
   l.xs = l.acts = 0;
-  l.granule_bytes = precision == MB200_PRECISION_FP8 ? 0 : (cap / kPadBf16 + 1) * 4;
+  // arrival counters per 16-row granule (fused dispatch) and completion counters per token
+  // block (fused combine push), adjacent so that one memset clears both
+  l.granule_bytes = (cap / kPadBf16 + 1) * 4;
   l.granules = take(l.granule_bytes);
+  l.block_bytes = (cap / kPadBf16 + 1) * 4;
+  l.blocks = take(l.block_bytes);
+  l.counter_span = l.blocks + l.block_bytes - l.granules;
   l.xq_tok = l.xs_tok = 0;
   if (precision == MB200_PRECISION_FP8) {
     l.xs = take(int64_t(hidden / 128) * cap * 4);
@@ -530,12 +535,31 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
   PeerTable self_q{}, self_s{};
   self_q.ptr[0] = xq_tok;
   self_s.ptr[0] = xs_tok;
-  if ((rc = launch_gather_rows_peer_fp8(self_q, self_s, 0, 1, int(tokens), topk, sched, local_experts, hidden, xq,
-                                        xs_t, cap, s))) return rc;
+  FusedDispatchFp8 disp{};
+  if (pad == kTileM) {
+    // 128-row-tile kernel: the gather runs inside the gate/up GEMM kernel (helper warps); only its
+    // counters are reset here
+    disp.xq = self_q;
+    disp.xs = self_s;
+    disp.rank = 0;
+    disp.world = 1;
+    disp.tokens_per_rank = int(tokens);
+    disp.topk = topk;
+    disp.groups_per_row = hidden / 128;
+    disp.rows_out = reinterpret_cast<uint4*>(xq);
+    disp.scales_t_out = xs_t;
+    disp.granule_done = reinterpret_cast<int*>(ws + l.granules);
+    disp.enabled = 1;
+    MB200_CHECK_CUDA(cudaMemsetAsync(disp.granule_done, 0, size_t(l.granule_bytes), s));
+  } else if ((rc = launch_gather_rows_peer_fp8(self_q, self_s, 0, 1, int(tokens), topk, sched, local_experts, hidden,
+                                               xq, xs_t, cap, s))) {
+    return rc;
+  }
   mark_stage(2, s);
   if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, xq, xs_t, cap, w1, w1_scale, local_experts, hidden, intermediate,
                                sched.counts, sched.mtile_prefix, sched.sorted_ids, nullptr, actq, acts_t, status,
-                               device, s, reinterpret_cast<unsigned long long*>(status + 8), pad))) return rc;
+                               device, s, reinterpret_cast<unsigned long long*>(status + 8), pad,
+                               disp.enabled ? &disp : nullptr))) return rc;
   mark_stage(3, s);
   if ((rc = run_gemm_stage_fp8(kDownWeighted, actq, acts_t, cap, w2, w2_scale, local_experts, hidden, intermediate,
                                sched.counts, sched.mtile_prefix, sched.sorted_ids, topk_weights, y, nullptr, status,

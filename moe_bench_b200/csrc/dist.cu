@@ -27,7 +27,7 @@ namespace {
 int64_t up1k(int64_t v) { return (v + 1023) / 1024 * 1024; }
 
 struct SymLayout {
-  int64_t flags, ids, weights, payload, payload_scales, partial, total;
+  int64_t flags, ids, weights, payload, payload_scales, partial, yrecv, total;
 };
 
 SymLayout make_sym_layout(int precision, int64_t tokens, int hidden, int topk, int world) {
@@ -40,6 +40,9 @@ SymLayout make_sym_layout(int precision, int64_t tokens, int hidden, int topk, i
   l.payload = take(tokens * hidden * (precision == MB200_PRECISION_FP8 ? 1 : 2));
   l.payload_scales = take(precision == MB200_PRECISION_FP8 ? tokens * (hidden / 128) * 4 : 0);
   l.partial = take(int64_t(world) * tokens * hidden * 2);
+  // expert parallel with the fused combine push: one weighted row per assignment of this
+  // rank's tokens, written by whichever rank owns the expert
+  l.yrecv = take(tokens * topk * hidden * 2);
   l.total = off;
   return l;
 }
@@ -163,16 +166,32 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   if ((rc = launch_align(ids_all, all_tokens * topk, expert_parallel ? expert_map : nullptr, local_experts, sched,
                          cap, reinterpret_cast<int*>(ws + l.scratch), s))) return rc;
   mark_stage(1, s);
-  FusedDispatch disp{};  // bf16: the dispatch pulls run inside the gate/up GEMM kernel
+  // Which fused forms apply: the 16-bit kernels and the fp8 128-row-tile kernel have dispatch and
+  // push warps; the fp8 tokens-on-columns kernel (few rows per expert) keeps separate stages.
+  const bool fp8_rows = fp8 && pad == kTileM;
+  const bool fused_kernels = !fp8 || fp8_rows;
+  const bool push_combine = expert_parallel && fused_kernels;
+  int* granule_done = reinterpret_cast<int*>(ws + l.granules);
+  int* block_done = reinterpret_cast<int*>(ws + l.blocks);
+  if (fused_kernels) MB200_CHECK_CUDA(cudaMemsetAsync(granule_done, 0, size_t(l.counter_span), s));
+  FusedDispatch disp{};       // 16-bit: the dispatch pulls run inside the gate/up GEMM kernel
+  FusedDispatchFp8 disp8{};   // fp8, 128-row tiles: likewise (e4m3 rows + scales)
+  const PeerTable payload = offset_table(symmetric_ptrs, world, sl.payload);
+  const PeerTable payload_scales = offset_table(symmetric_ptrs, world, sl.payload_scales);
   if (expert_parallel) {
     // a token has about one expert per rank: pull each needed row straight into its sorted slot
-    if (fp8) {
-      if ((rc = launch_gather_rows_peer_fp8(offset_table(symmetric_ptrs, world, sl.payload),
-                                        offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world,
-                                        int(tokens), topk, sched, local_experts, hidden, ws + l.xg,
-                                        reinterpret_cast<float*>(ws + l.xs), cap, s))) return rc;
+    if (fp8_rows) {
+      disp8.xq = payload;
+      disp8.xs = payload_scales;
+      disp8.rank = rank;
+      disp8.world = world;
+      disp8.tokens_per_rank = int(tokens);
+    } else if (fp8) {
+      if ((rc = launch_gather_rows_peer_fp8(payload, payload_scales, rank, world, int(tokens), topk, sched,
+                                            local_experts, hidden, ws + l.xg, reinterpret_cast<float*>(ws + l.xs),
+                                            cap, s))) return rc;
     } else {
-      disp.src = offset_table(symmetric_ptrs, world, sl.payload);
+      disp.src = payload;
       disp.rank = rank;
       disp.world = world;
       disp.tokens_per_rank = int(tokens);
@@ -184,17 +203,24 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
     const int64_t eb = fp8 ? 1 : 2;
     char* x_all = ws + l.total + 2 * routing_bytes;
     char* xs_all = x_all + up1k(all_tokens * hidden * eb);
-    if ((rc = launch_gather_blocks_peer(offset_table(symmetric_ptrs, world, sl.payload), rank, world,
-                                        tokens * hidden * eb, x_all, s))) return rc;
-    if (fp8 && (rc = launch_gather_blocks_peer(offset_table(symmetric_ptrs, world, sl.payload_scales), rank, world,
-                                               tokens * (hidden / 128) * 4, xs_all, s))) return rc;
+    if ((rc = launch_gather_blocks_peer(payload, rank, world, tokens * hidden * eb, x_all, s))) return rc;
+    if (fp8 && (rc = launch_gather_blocks_peer(payload_scales, rank, world, tokens * (hidden / 128) * 4, xs_all, s)))
+      return rc;
     if (fp8) {
+      // one "rank" holding all W*T tokens in ring order
       PeerTable local_x{}, local_s{};
       local_x.ptr[0] = x_all;
       local_s.ptr[0] = xs_all;
-      // one "rank" holding all W*T tokens in ring order
-      if ((rc = launch_gather_rows_peer_fp8(local_x, local_s, 0, 1, int(all_tokens), topk, sched, local_experts,
-                                        hidden, ws + l.xg, reinterpret_cast<float*>(ws + l.xs), cap, s))) return rc;
+      if (fp8_rows) {
+        disp8.xq = local_x;
+        disp8.xs = local_s;
+        disp8.rank = 0;
+        disp8.world = 1;
+        disp8.tokens_per_rank = int(all_tokens);
+      } else if ((rc = launch_gather_rows_peer_fp8(local_x, local_s, 0, 1, int(all_tokens), topk, sched, local_experts,
+                                                   hidden, ws + l.xg, reinterpret_cast<float*>(ws + l.xs), cap, s))) {
+        return rc;
+      }
     } else {
       disp.src.ptr[0] = x_all;
       disp.rank = 0;
@@ -206,24 +232,47 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
     disp.topk = topk;
     disp.vec_per_row = hidden / 8;
     disp.rows_out = reinterpret_cast<uint4*>(ws + l.xg);
-    disp.granule_done = reinterpret_cast<int*>(ws + l.granules);
+    disp.granule_done = granule_done;
     disp.granule_target = kDispatchWarpsPerCta;
-  disp.enabled = kDispatchFused;
-    MB200_CHECK_CUDA(cudaMemsetAsync(disp.granule_done, 0, size_t(l.granule_bytes), s));
+    disp.enabled = kDispatchFused;
+  } else if (fp8_rows) {
+    disp8.topk = topk;
+    disp8.groups_per_row = hidden / 128;
+    disp8.rows_out = reinterpret_cast<uint4*>(ws + l.xg);
+    disp8.scales_t_out = reinterpret_cast<float*>(ws + l.xs);
+    disp8.granule_done = granule_done;
+    disp8.enabled = 1;
   }
   mark_stage(2, s);
-  // 4. grouped GEMMs and the local pre-reduction into `partial`
+  // 4. grouped GEMMs.  Expert parallel, fused kernels: the down GEMM's push warps send every
+  // finished row to the rank that owns its token; otherwise the contributions of a token that
+  // landed on this rank are pre-reduced into one row of `partial`.
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.y);
+  FusedPush push{};
+  if (push_combine) {
+    push.dst = offset_table(symmetric_ptrs, world, sl.yrecv);
+    push.rank = rank;
+    push.world = world;
+    push.tokens_per_rank = int(tokens);
+    push.topk = topk;
+    push.vec_per_row = hidden / 8;
+    push.own_rows = int(tokens) * topk;
+    push.rows_in = reinterpret_cast<const uint4*>(y);
+    push.block_done = block_done;
+    push.enabled = 1;
+  }
   if (fp8) {
     if ((rc = run_gemm_stage_fp8(kGateUpSwiglu, ws + l.xg, reinterpret_cast<float*>(ws + l.xs), cap, w1, w1_scale,
                                  local_experts, hidden, intermediate, sched.counts, sched.mtile_prefix,
                                  sched.sorted_ids, nullptr, ws + l.act, reinterpret_cast<float*>(ws + l.acts), status,
-                                 device, s, reinterpret_cast<unsigned long long*>(status + 8), pad))) return rc;
+                                 device, s, reinterpret_cast<unsigned long long*>(status + 8), pad,
+                                 fp8_rows ? &disp8 : nullptr))) return rc;
     mark_stage(3, s);
     if ((rc = run_gemm_stage_fp8(kDownWeighted, ws + l.act, reinterpret_cast<float*>(ws + l.acts), cap, w2, w2_scale,
                                  local_experts, hidden, intermediate, sched.counts, sched.mtile_prefix,
                                  sched.sorted_ids, weights_all, y, nullptr, status, device, s,
-                                 reinterpret_cast<unsigned long long*>(status + 12), pad))) return rc;
+                                 reinterpret_cast<unsigned long long*>(status + 12), pad, nullptr,
+                                 push_combine ? &push : nullptr))) return rc;
   } else {
     if ((rc = run_gemm_stage(kGateUpSwiglu, ws + l.xg, cap, w1, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, nullptr, ws + l.act, status, device, s,
@@ -231,18 +280,29 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
     mark_stage(3, s);
     if ((rc = run_gemm_stage(kDownWeighted, ws + l.act, cap, w2, local_experts, hidden, intermediate, sched.counts,
                              sched.mtile_prefix, sched.sorted_ids, weights_all, y, status, device, s,
-                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16))) return rc;
+                             reinterpret_cast<unsigned long long*>(status + 12), nullptr, fp16,
+                             push_combine ? &push : nullptr))) return rc;
   }
   mark_stage(4, s);
-  if ((rc = launch_combine_bf16(y, sched.inverse, int(all_tokens), topk, hidden,
-                                reinterpret_cast<__nv_bfloat16*>(sym + sl.partial), s, fp16))) return rc;
-  // 5. combine across ranks
-  if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 2, status, s))) return rc;
-  if ((rc = launch_reduce_partials(offset_table(symmetric_ptrs, world, sl.partial), rank, world, int(tokens), topk,
-                                   topk_ids, expert_parallel ? local_experts : 0, hidden,
-                                   reinterpret_cast<__nv_bfloat16*>(out), s, fp16))) return rc;
-  // peers may still be reading this rank's buffers: nobody restages before all are done
-  rc = launch_peer_barrier(flags, rank, world, seq_base + 3, status, s);
+  if (push_combine) {
+    // 5. every rank's pushes have landed; sum the k rows of each own token.  Two barriers per
+    // forward are enough: peers push again only after the next forward's first barrier, which
+    // this rank reaches after this combine, and tokens are restaged only after every peer has
+    // passed this barrier, i.e. has finished pulling them.
+    if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 2, status, s))) return rc;
+    rc = launch_combine_bf16(reinterpret_cast<const __nv_bfloat16*>(sym + sl.yrecv), nullptr, int(tokens), topk,
+                             hidden, reinterpret_cast<__nv_bfloat16*>(out), s, fp16);
+  } else {
+    if ((rc = launch_combine_bf16(y, sched.inverse, int(all_tokens), topk, hidden,
+                                  reinterpret_cast<__nv_bfloat16*>(sym + sl.partial), s, fp16))) return rc;
+    // 5. combine across ranks
+    if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 2, status, s))) return rc;
+    if ((rc = launch_reduce_partials(offset_table(symmetric_ptrs, world, sl.partial), rank, world, int(tokens), topk,
+                                     topk_ids, expert_parallel ? local_experts : 0, hidden,
+                                     reinterpret_cast<__nv_bfloat16*>(out), s, fp16))) return rc;
+    // peers may still be reading this rank's buffers: nobody restages before all are done
+    rc = launch_peer_barrier(flags, rank, world, seq_base + 3, status, s);
+  }
   mark_stage(5, s);
   return rc;
 }

@@ -182,8 +182,11 @@ struct Layout {
   int64_t status, counts, prefix, sorted, inverse, scratch, xg, act, y, total;
   int64_t xs, acts;  // fp8 only: transposed activation scales [K/128][cap], [N/128][cap]
   int64_t xq_tok, xs_tok;  // fp8 only: the tokens quantised once, [T][K] e4m3 and [T][K/128] scales
-  int64_t granules;  // bf16 only: arrival counter per 16-row granule of the sorted row buffer
+  int64_t granules;  // arrival counter per 16-row granule of the sorted row buffer (fused dispatch)
   int64_t granule_bytes;
+  int64_t blocks;    // completion counter per token block (fused combine push)
+  int64_t block_bytes;
+  int64_t counter_span;  // bytes from `granules` to the end of `blocks`
 };
 Layout make_layout(int precision, int64_t tokens, int hidden, int intermediate, int local_experts, int topk,
                    int pad_rows);

@@ -1,5 +1,6 @@
 // Row-wise, bandwidth-bound stages around the grouped GEMMs:
-//   combine:       out[t, :] = sum over the k local assignments of token t of
+//   combine:       (inverse == nullptr: every assignment is present)
+//                  out[t, :] = sum over the k local assignments of token t of
 //                  the already weighted rows y[t*k + j, :], fp32 sum, bf16 store
 //                  (reference.py:180-182).
 //   group_quant:   per row, per 128-wide group dynamic e4m3 quantisation of
@@ -29,7 +30,7 @@ __global__ void combine_bf16_kernel(const uint4* __restrict__ y, const int* __re
       for (int u = 0; u < 8; ++u) {
         const int64_t n = t * topk + j0 + u;
         // an expert on another rank contributes zero
-        have[u] = j0 + u < topk && __ldg(inverse + n) >= 0;
+        have[u] = j0 + u < topk && (inverse == nullptr || __ldg(inverse + n) >= 0);
         if (have[u]) val[u] = __ldg(y + n * vec_per_row + v);
       }
 #pragma unroll
