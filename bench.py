@@ -22,8 +22,8 @@ latency; ``ms_per_step`` is that latency.  Prints ONE JSON line on rank 0.
 
 With N > 1 the layer runs expert-parallel over the N GPUs (the reference's
 distributed EP mode): rank r owns 256/N experts and its own shard of T tokens,
-token dispatch and the weighted combine cross NVLink inside the library's
-kernels.  Per-GPU work is fixed (weak scaling); the value is the sum over ranks
+token dispatch (pulls) and the weighted combine (pushes) cross NVLink inside the
+library's GEMM kernels.  Per-GPU work is fixed (weak scaling); the value is the sum over ranks
 divided by the slowest rank's time.
 """
 
@@ -366,7 +366,7 @@ def _config_dict(tokens: int, world: int, precision: str = "bf16", mode: str = "
         "intermediate": INTER, "experts": EXPERTS, "topk": TOPK, "routing": distribution, "seed": 0,
         "parallelism": "single GPU, all experts local" if world == 1 else
                        (f"ep{world}: {EXPERTS // world} experts and {tokens} own tokens per GPU, "
-                        "dispatch/combine by P2P pulls over NVLink" if mode == "ep" else
+                        "dispatch by P2P pulls and combine by P2P pushes over NVLink, both inside the GEMM kernels" if mode == "ep" else
                         f"tp{world}: all experts, intermediate/{world} columns and {tokens} own tokens per GPU, "
                         "token gather and output reduce by P2P pulls over NVLink"),
         "l2": f"inputs larger than L2: {wgb} GB of expert weights are streamed every step",
@@ -607,7 +607,7 @@ def _dispatch_exact(leg: Leg) -> dict:
     remote_rows = int((tok >= t).sum().item()) if world > 1 else 0
     row_bytes = HIDDEN * eb + (HIDDEN // 128 * 4 if fp8 else 0)
     return {"exact": env.all_agree(ok), "rows": int(valid.numel()), "remote_rows": remote_rows,
-            "remote_bytes": remote_rows * row_bytes}
+            "remote_bytes": remote_rows * row_bytes, "pad_rows": lay["pad_rows"]}
 
 
 def _repeat_identical(leg: Leg, first, n: int = 30) -> bool:
@@ -725,30 +725,38 @@ def _nvlink_report(leg: Leg, disp: dict, stage_ms) -> dict:
         return None
     names = dict(zip(leg.stage_names, stage_ms))
     fp8 = leg.precision == "fp8"
-    # combine: one 16-bit row per (own token, remote rank that owns one of its experts); TP: one per remote rank
+    eb = 1 if fp8 else 2
+    row_bytes = HIDDEN * eb + (HIDDEN // 128 * 4 if fp8 else 0)
+    fused = not fp8 or disp["pad_rows"] == 128   # kernels with dispatch / push warps
     if leg.tp:
-        pairs = leg.tokens * (env.world - 1)
+        d_bytes = (env.world - 1) * leg.tokens * row_bytes
+        d_ms, d_note = names["dispatch"], "token blocks of all peers pulled once, before the GEMM"
+        c_bytes = leg.tokens * (env.world - 1) * HIDDEN * 2
+        c_ms, c_note = names["combine"], ("one pre-reduced row per own token from every peer, pulled and summed; "
+                                          "the stage includes its barriers")
     else:
         owner = (leg.ids // leg.e_local).long()
-        mask = torch.zeros(leg.tokens, env.world, dtype=torch.bool, device=env.dev)
-        mask.scatter_(1, owner, True)
-        mask[:, env.rank] = False
-        pairs = int(mask.sum().item())
-    comb_bytes = pairs * HIDDEN * 2
-    if leg.tp:
-        d_ms, d_note = names["dispatch"], "token blocks of all peers pulled once, before the GEMM"
-    elif fp8:
-        d_ms, d_note = names["dispatch"], "e4m3 rows + scales pulled by the dispatch stage"
-    else:
-        d_ms, d_note = names["gate_up_gemm"], ("rows pulled by the dispatch warps inside the gate/up GEMM kernel: "
-                                               "rate over the whole kernel, a lower bound")
-    c_ms = names["combine"]
+        remote_assign = int((owner != env.rank).sum().item())
+        d_bytes = disp["remote_bytes"]
+        if fused:
+            d_ms, d_note = names["gate_up_gemm"], ("rows pulled by the dispatch warps inside the gate/up GEMM kernel: "
+                                                   "rate over the whole kernel, a lower bound")
+            c_bytes = remote_assign * HIDDEN * 2
+            c_ms, c_note = names["down_gemm"], ("one weighted row per assignment of an own token whose expert is "
+                                                "remote, pushed by the down GEMM kernel of the expert rank while it "
+                                                "computes: rate over the whole kernel, a lower bound")
+        else:
+            d_ms, d_note = names["dispatch"], "e4m3 rows + scales pulled by the dispatch stage"
+            mask = torch.zeros(leg.tokens, env.world, dtype=torch.bool, device=env.dev)
+            mask.scatter_(1, owner, True)
+            mask[:, env.rank] = False
+            c_bytes = int(mask.sum().item()) * HIDDEN * 2
+            c_ms, c_note = names["combine"], ("one pre-reduced row per (own token, remote expert rank), pulled and "
+                                              "summed; the stage includes its barriers")
     return {
         "peak_gbs_per_direction": 770.0,
-        "dispatch": {"bytes_in": disp["remote_bytes"], "ms": d_ms, "gbs": disp["remote_bytes"] / (d_ms * 1e-3) / 1e9,
-                     "note": d_note},
-        "combine": {"bytes_in": comb_bytes, "ms": c_ms, "gbs": comb_bytes / (c_ms * 1e-3) / 1e9,
-                    "note": "partial rows of own tokens from the expert ranks; the stage includes its barriers"},
+        "dispatch": {"bytes_in": d_bytes, "ms": d_ms, "gbs": d_bytes / (d_ms * 1e-3) / 1e9, "note": d_note},
+        "combine": {"bytes_in": c_bytes, "ms": c_ms, "gbs": c_bytes / (c_ms * 1e-3) / 1e9, "note": c_note},
     }
 
 
@@ -1044,7 +1052,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         if world == 1:      # align, [fp8: quantise + row gather], gate/up GEMM (16-bit: gather fused), down GEMM, combine
             kernels_per_step = n_align + 3 + (2 if fp8 else 0)
         else:
-            kernels_per_step = _dist_kernels_per_step(n_align, fp8, leg.tp)
+            kernels_per_step = _dist_kernels_per_step(n_align, fp8, leg.tp, not fp8 or disp["pad_rows"] == 128)
         line = {
             "metric": METRIC, "value": flops_step * world / (ms_step * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
@@ -1094,9 +1102,13 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
-def _dist_kernels_per_step(n_align: int, fp8: bool, tp: bool) -> int:
-    """Kernels of one distributed forward: barriers, routing gather, align, [fp8: quantise, row
+def _dist_kernels_per_step(n_align: int, fp8: bool, tp: bool, fused: bool) -> int:
+    """Kernels of one distributed forward.  Expert parallel with the fused kernels: 2 barriers,
+    routing gather, align, [fp8: quantise], gate/up GEMM (with the dispatch), down GEMM (with the
+    combine push), final sum.  Otherwise: 3 barriers, routing gather, align, [fp8: quantise, row
     gather], [TP: block gathers], two GEMMs, local pre-reduce, partial reduce."""
+    if not tp and fused:
+        return n_align + 2 + 1 + 2 + 1 + (1 if fp8 else 0)
     n = n_align + 3 + 5 + (2 if fp8 else 0)
     if tp:
         n += 2 if fp8 else 1
