@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define MB200_ABI_VERSION 3
+#define MB200_ABI_VERSION 4
 #define MB200_PRECISION_BF16 0
 #define MB200_PRECISION_FP8 1
 #define MB200_PRECISION_FP16 2 /* the bf16 data flow with IEEE half operands and outputs */
@@ -237,8 +237,16 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
  *
  * symmetric_ptrs[world]: base pointers, valid in THIS process, of one buffer per
  * rank with mb200_dist_symmetric_bytes() bytes, 1024-byte aligned, zero-filled
- * once after allocation; entry [rank] is this rank's own buffer.  The library
- * only loads from peers' buffers and stores 4-byte barrier flags into them.
+ * once after allocation; entry [rank] is this rank's own buffer.  Token rows are
+ * LOADED from the peers' buffers (dispatch); what the library STORES into a
+ * peer's buffer are 4-byte barrier flags and, expert parallel, the weighted
+ * output rows of that peer's tokens (combine by push into its receive area).
+ * One forward = stage own tokens and routing | barrier | routing of all ranks,
+ * sort-and-pad | gate/up GEMM whose helper warps pull the rows it needs over
+ * NVLink | down GEMM whose helper warps push finished rows to the tokens' owners
+ * | barrier | sum of the k rows of every own token.  (Tensor parallel, and fp8
+ * with at most 24 rows per expert: token blocks / rows are gathered before the
+ * GEMM and pre-reduced partial rows are pulled after a barrier, three barriers.)
  * seq_base: a counter that is equal on all ranks and grows by
  * MB200_DIST_SEQ_STRIDE per call (barrier sequence numbers are never reset).
  * All ranks must make the same calls in the same order.  A barrier that does not
@@ -286,6 +294,13 @@ int mb200_set_stage_events(void* const* events, int count);
  * in the kernel during the last call; cycles/ns is the SM clock in GHz the kernel
  * really ran at (a power-capped part runs tensor kernels far below the clock
  * that the management library reports between kernels). */
+
+/* Decomposition aid (the reference times dispatch and combine without the GEMMs in
+ * tools/time_dispatch.py and tools/analyze_overlap.py:88-100).  While enabled for
+ * the calling thread, the forward entry points launch the same kernels but with
+ * zero K steps: routing exchange, barriers, dispatch of rows, stores and combine
+ * traffic all happen, the arithmetic does not, and the outputs mean nothing. */
+int mb200_set_comm_only(int enabled);
 
 /* Copies the workspace status word to the host after synchronising `stream`
  * (0 = no kernel gave up a wait).  Not capturable. */

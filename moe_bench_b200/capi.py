@@ -16,7 +16,7 @@ import torch
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libmoe_bench_b200.so")
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 PRECISION_BF16 = 0
 PRECISION_FP8 = 1
 PRECISION_FP16 = 2
@@ -81,6 +81,7 @@ SIGNATURES = {
     "mb200_ipc_close": (c_i32, [c_vp]),
     "mb200_ipc_free": (c_i32, [c_vp]),
     "mb200_set_stage_events": (c_i32, [c_vp, c_i32]),
+    "mb200_set_comm_only": (c_i32, [c_i32]),
     "mb200_read_status": (c_i32, [c_vp, c_vp, c_vp]),
 }
 
@@ -391,6 +392,11 @@ def set_stage_events(events) -> None:
         return
     arr = (ctypes.c_void_p * len(events))(*[ev.cuda_event for ev in events])
     _check(load().mb200_set_stage_events(arr, len(events)), "set_stage_events")
+
+
+def set_comm_only(enabled: bool) -> None:
+    """Forward calls from this thread move data only (GEMM kernels run with zero K steps)."""
+    _check(load().mb200_set_comm_only(1 if enabled else 0), "set_comm_only")
 
 
 def read_kernel_clocks(workspace: torch.Tensor) -> dict:

@@ -17,6 +17,7 @@ thread_local char g_last_error[512] = "";
 constexpr int kStageEvents = 6;
 thread_local cudaEvent_t g_stage_events[kStageEvents] = {};
 thread_local int g_stage_event_count = 0;
+thread_local int g_comm_only = 0;
 
 }
 
@@ -194,6 +195,7 @@ int run_gemm_stage(int mode, const void* a, int64_t cap, const void* w, int loca
     g.b_half_offset = 0;
     g.out_cols = hidden;
   }
+  if (g_comm_only) g.k_iters = 0;  // decomposition: data movement only (see mb200_set_comm_only)
   FusedDispatch none{};
   FusedPush no_push{};
   return launch_grouped_gemm_bf16(GemmMode(mode), map_w, maps_t, g, dispatch ? *dispatch : none,
@@ -260,6 +262,7 @@ int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t 
   }
   MB200_REQUIRE(!cols || (!dispatch && !push), kInvalidArgument,
                 "fp8: fused dispatch / push exist only in the 128-row-tile kernel");
+  if (g_comm_only) g.k_blocks = 0;  // decomposition: data movement only (see mb200_set_comm_only)
   if (cols) return launch_grouped_gemm_fp8_cols(GemmMode(mode), map_b, maps_t, g, device, stream);
   const FusedDispatchFp8 no_disp{};
   const FusedPush no_push{};
@@ -576,6 +579,11 @@ int mb200_set_stage_events(void* const* events, int count) {
   for (int i = 0; i < kStageEvents; ++i)
     g_stage_events[i] = i < count ? reinterpret_cast<cudaEvent_t>(events[i]) : nullptr;
   g_stage_event_count = count;
+  return kOk;
+}
+
+int mb200_set_comm_only(int enabled) {
+  g_comm_only = enabled ? 1 : 0;
   return kOk;
 }
 

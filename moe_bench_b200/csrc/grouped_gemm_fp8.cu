@@ -570,8 +570,8 @@ int launch_grouped_gemm_fp8(GemmMode mode, const CUtensorMap& map_a, const CUten
                             int device, cudaStream_t stream) {
   MB200_REQUIRE(args.num_experts >= 1 && args.num_experts <= kMaxExperts, kUnsupportedShape,
                 "grouped_gemm_fp8: %d local experts, supported 1..%d", args.num_experts, kMaxExperts);
-  MB200_REQUIRE(args.k_blocks >= 1 && args.k_blocks <= kMaxKBlocks, kUnsupportedShape,
-                "grouped_gemm_fp8: %d K blocks of 128, supported 1..%d", args.k_blocks, kMaxKBlocks);
+  MB200_REQUIRE(args.k_blocks >= 0 && args.k_blocks <= kMaxKBlocks, kUnsupportedShape,
+                "grouped_gemm_fp8: %d K blocks of 128, supported 0..%d", args.k_blocks, kMaxKBlocks);
   MB200_REQUIRE(args.out_cols % 16 == 0, kUnsupportedShape,
                 "grouped_gemm_fp8: output row length %d must be a multiple of 16", args.out_cols);
   MB200_REQUIRE((reinterpret_cast<uintptr_t>(args.a_scale_t) & 15) == 0 && args.row_capacity % kTileM == 0,

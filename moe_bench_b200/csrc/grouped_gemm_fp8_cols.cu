@@ -466,8 +466,8 @@ int launch_grouped_gemm_fp8_cols(GemmMode mode, const CUtensorMap& map_w, const 
                                  const GemmFp8Args& args, int device, cudaStream_t stream) {
   MB200_REQUIRE(args.num_experts >= 1 && args.num_experts <= kMaxExperts, kUnsupportedShape,
                 "grouped_gemm_fp8: %d local experts, supported 1..%d", args.num_experts, kMaxExperts);
-  MB200_REQUIRE(args.k_blocks >= 1 && args.k_blocks <= kMaxKBlocks, kUnsupportedShape,
-                "grouped_gemm_fp8: %d K blocks of 128, supported 1..%d", args.k_blocks, kMaxKBlocks);
+  MB200_REQUIRE(args.k_blocks >= 0 && args.k_blocks <= kMaxKBlocks, kUnsupportedShape,
+                "grouped_gemm_fp8: %d K blocks of 128, supported 0..%d", args.k_blocks, kMaxKBlocks);
   const int sms = device_sm_count(device);
   MB200_REQUIRE(sms > 0, kCudaError, "grouped_gemm_fp8: cannot read the SM count of device %d", device);
   auto kernel = mode == kGateUpSwiglu ? grouped_gemm_fp8_cols_kernel<kGateUpSwiglu>

@@ -208,6 +208,16 @@ class B200Scheme(DistributedScheme):
         self._seq += capi.DIST_SEQ_STRIDE
         return self._out
 
+    def run_comm_only(self) -> torch.Tensor:
+        """One forward with the arithmetic switched off: staging, barriers, routing exchange,
+        dispatch of rows and combine traffic only (for the decomposition of a step into
+        computation and communication; the returned tensor means nothing)."""
+        capi.set_comm_only(True)
+        try:
+            return self.run()
+        finally:
+            capi.set_comm_only(False)
+
     def device_status(self) -> int:
         return capi.read_status(self._workspace)
 
