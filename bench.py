@@ -845,6 +845,11 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    # fp8 activation scales: the format the reference uses on this box (vLLM decides), in the
+    # library and in the oracle that checks it
+    from oracle import moe_oracle as O
+
+    O.FP8_SCALE_FORMAT = capi.use_reference_fp8_scale_format()
     tokens, steps, warmup = args.tokens, args.steps, args.warmup
     fp8 = args.precision == "fp8"
     leg = Leg(env, args.precision, tokens, args.mode, args.distribution, routing=args.routing)
@@ -1076,6 +1081,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "layer_roofline_ms": layer["layer_roofline_ms"], "layer_roofline_frac": layer["layer_roofline_frac"],
             "latency_us": ms_step * 1e3,
             **ver, "dispatch_bytes_exact": disp["exact"], "repeat30_identical": same30, "nvlink": nvlink,
+            "fp8_activation_scales": O.FP8_SCALE_FORMAT,
+            "fp8_activation_scales_note": "fp8 legs: the format vLLM's quantiser (which the reference calls) uses "
+                                          "on this box: ue8m0 = amax/448 rounded up to a power of two",
         }
         line["gpu_baseline"] = gpu_base
     default_workload = (tokens == 8192 and args.precision == "bf16" and args.mode == "ep"

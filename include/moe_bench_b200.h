@@ -295,6 +295,20 @@ int mb200_set_stage_events(void* const* events, int count);
  * really ran at (a power-capped part runs tensor kernels far below the clock
  * that the management library reports between kernels). */
 
+/* Format of the fp8 ACTIVATION scales (one per token per 128 elements) that the
+ * calling thread's later calls compute, in the input quantiser and in the gate/up
+ * GEMM's re-quantiser.  The reference obtains them from vLLM's
+ * per_token_group_quant_fp8 (reference.py:143-145,157-163), whose result depends
+ * on the platform: plain fp32 amax/448, or - when vLLM runs with DeepGEMM's E8M0
+ * scales, its default on Hopper and Blackwell GPUs (vllm/utils/deep_gemm.py,
+ * is_deep_gemm_e8m0_used) - that value rounded up to a power of two.  To verify
+ * against the reference on a given box the library has to quantise the way the
+ * reference does there; moe_bench_b200.plugin asks vLLM when it is importable.
+ * Weight scales are inputs and are used as given.  Default: MB200_FP8_SCALES_FP32. */
+#define MB200_FP8_SCALES_FP32 0
+#define MB200_FP8_SCALES_UE8M0 1
+int mb200_set_fp8_scale_format(int format);
+
 /* Decomposition aid (the reference times dispatch and combine without the GEMMs in
  * tools/time_dispatch.py and tools/analyze_overlap.py:88-100).  While enabled for
  * the calling thread, the forward entry points launch the same kernels but with

@@ -81,6 +81,7 @@ SIGNATURES = {
     "mb200_ipc_close": (c_i32, [c_vp]),
     "mb200_ipc_free": (c_i32, [c_vp]),
     "mb200_set_stage_events": (c_i32, [c_vp, c_i32]),
+    "mb200_set_fp8_scale_format": (c_i32, [c_i32]),
     "mb200_set_comm_only": (c_i32, [c_i32]),
     "mb200_read_status": (c_i32, [c_vp, c_vp, c_vp]),
 }
@@ -392,6 +393,41 @@ def set_stage_events(events) -> None:
         return
     arr = (ctypes.c_void_p * len(events))(*[ev.cuda_event for ev in events])
     _check(load().mb200_set_stage_events(arr, len(events)), "set_stage_events")
+
+
+FP8_SCALE_FORMATS = {"fp32": 0, "ue8m0": 1}
+
+
+def set_fp8_scale_format(fmt: str) -> None:
+    """Format of the fp8 activation scales computed by later calls from this thread:
+    ``"fp32"`` (amax/448) or ``"ue8m0"`` (rounded up to a power of two)."""
+    if fmt not in FP8_SCALE_FORMATS:
+        raise MB200Error(f"fp8 scale format {fmt!r}: expected one of {sorted(FP8_SCALE_FORMATS)}")
+    _check(load().mb200_set_fp8_scale_format(FP8_SCALE_FORMATS[fmt]), "set_fp8_scale_format")
+
+
+def reference_fp8_scale_format() -> str:
+    """What the reference's activation quantiser does on this box.  The reference calls
+    vLLM's ``per_token_group_quant_fp8`` without saying which scale format it wants
+    (reference.py:143-145), and vLLM then follows ``is_deep_gemm_e8m0_used()``: power-of-two
+    scales on GPUs where its DeepGEMM path is enabled (Hopper, Blackwell), fp32 elsewhere.
+    Without vLLM there is no reference to match and the plain fp32 format applies."""
+    if not torch.cuda.is_available():
+        return "fp32"
+    try:
+        from vllm.utils.deep_gemm import is_deep_gemm_e8m0_used
+
+        return "ue8m0" if is_deep_gemm_e8m0_used() else "fp32"
+    except Exception:  # noqa: BLE001
+        return "fp32"
+
+
+def use_reference_fp8_scale_format() -> str:
+    """Select, for this thread's direct calls, the scale format the reference uses on this
+    box; returns it ("fp32" or "ue8m0") so that a checker can compute in the same format."""
+    fmt = reference_fp8_scale_format()
+    set_fp8_scale_format(fmt)
+    return fmt
 
 
 def set_comm_only(enabled: bool) -> None:

@@ -18,8 +18,11 @@ constexpr int kStageEvents = 6;
 thread_local cudaEvent_t g_stage_events[kStageEvents] = {};
 thread_local int g_stage_event_count = 0;
 thread_local int g_comm_only = 0;
+thread_local int g_fp8_ue8m0 = 0;
 
 }
+
+int fp8_scale_ue8m0() { return g_fp8_ue8m0; }
 
 void mark_stage(int i, cudaStream_t s) {
   if (i < g_stage_event_count && g_stage_events[i]) cudaEventRecord(g_stage_events[i], s);
@@ -218,6 +221,7 @@ int run_gemm_stage_fp8(int mode, const void* a, const float* a_scale_t, int64_t 
   CUtensorMap map_a, map_b;
   GemmFp8Args g{};
   g.clock_probe = clock_probe;
+  g.ue8m0 = g_fp8_ue8m0;
   const bool cols = pad_rows == kPadBf16;  // schedule padded to 16 rows: tokens-on-columns kernel
   TokenMaps maps_t;
   if (cols) {
@@ -314,7 +318,7 @@ int mb200_align(const int32_t* topk_ids, int64_t tokens, int topk, const int32_t
 int mb200_group_quant_fp8(const void* x, int64_t rows, int hidden, void* q, float* scales, void* stream) {
   MB200_REQUIRE(rows >= 0 && (rows == 0 || (x && q && scales)), kInvalidArgument, "group_quant: bad argument");
   return launch_group_quant_fp8(reinterpret_cast<const __nv_bfloat16*>(x), rows, hidden,
-                                reinterpret_cast<uint8_t*>(q), scales, hidden / 128, 0, as_stream(stream));
+                                reinterpret_cast<uint8_t*>(q), scales, hidden / 128, 0, as_stream(stream), g_fp8_ue8m0);
 }
 
 int mb200_grouped_gemm_bf16(int mode, const void* a, int64_t row_cap, const void* w, int local_experts,
@@ -534,7 +538,7 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
   uint8_t* xq_tok = reinterpret_cast<uint8_t*>(ws + l.xq_tok);
   float* xs_tok = reinterpret_cast<float*>(ws + l.xs_tok);
   if ((rc = launch_group_quant_fp8(reinterpret_cast<const __nv_bfloat16*>(hidden_states), tokens, hidden, xq_tok,
-                                   xs_tok, hidden / 128, 0, s))) return rc;
+                                   xs_tok, hidden / 128, 0, s, g_fp8_ue8m0))) return rc;
   PeerTable self_q{}, self_s{};
   self_q.ptr[0] = xq_tok;
   self_s.ptr[0] = xs_tok;
@@ -579,6 +583,13 @@ int mb200_set_stage_events(void* const* events, int count) {
   for (int i = 0; i < kStageEvents; ++i)
     g_stage_events[i] = i < count ? reinterpret_cast<cudaEvent_t>(events[i]) : nullptr;
   g_stage_event_count = count;
+  return kOk;
+}
+
+int mb200_set_fp8_scale_format(int format) {
+  MB200_REQUIRE(format == MB200_FP8_SCALES_FP32 || format == MB200_FP8_SCALES_UE8M0, kInvalidArgument,
+                "set_fp8_scale_format: unknown format %d", format);
+  g_fp8_ue8m0 = format == MB200_FP8_SCALES_UE8M0;
   return kOk;
 }
 

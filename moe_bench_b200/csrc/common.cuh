@@ -99,6 +99,18 @@ __device__ __forceinline__ uint4 pack_h16x8(const float (&acc)[8], int fp16) {
   return o;
 }
 
+// ---- fp8 activation scale ------------------------------------------------------
+// Scale of one 1x128 activation group from its absolute maximum (already clamped to
+// 1e-10): amax / 448 (the reference's quantiser, reference.py:143-145 -> vLLM
+// per_token_group_quant_fp8), or, when vLLM runs with DeepGEMM's E8M0 scales (its
+// default on Hopper / Blackwell), that value rounded UP to a power of two:
+// exp2(ceil(log2(.))), the formula of vLLM's quantiser.
+__device__ __forceinline__ float fp8_group_scale(float amax, int ue8m0) {
+  float scale = __fdiv_rn(amax, 448.0f);
+  if (ue8m0) scale = exp2f(ceilf(log2f(fmaxf(fabsf(scale), 1e-10f))));
+  return scale;
+}
+
 // ---- mbarrier -----------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

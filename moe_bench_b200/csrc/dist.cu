@@ -151,7 +151,8 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
   if (fp8) {
     if ((rc = launch_group_quant_fp8(reinterpret_cast<const __nv_bfloat16*>(hidden_states), tokens, hidden,
                                      reinterpret_cast<uint8_t*>(sym + sl.payload),
-                                     reinterpret_cast<float*>(sym + sl.payload_scales), hidden / 128, 0, s)))
+                                     reinterpret_cast<float*>(sym + sl.payload_scales), hidden / 128, 0, s,
+                                     fp8_scale_ue8m0())))
       return rc;
   } else {
     MB200_CHECK_CUDA(cudaMemcpyAsync(sym + sl.payload, hidden_states, tokens * int64_t(hidden) * 2,

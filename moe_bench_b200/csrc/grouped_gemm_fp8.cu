@@ -479,7 +479,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         ok = epilogue_barrier(&tail->epi_bar, epi_phase, ctx, lane);
         if (!ok) break;
         amax = fmaxf(fmaxf(amax, tail->amax[half ^ 1][r]), 1e-10f);
-        const float scale = __fdiv_rn(amax, 448.0f);
+        const float scale = fp8_group_scale(amax, args.ue8m0);
         const int out_col0 = tc.n_tile * 128 + half * 64;
         if (row_ok && out_col0 < args.out_cols) {
           uint8_t* dst = reinterpret_cast<uint8_t*>(args.out) + size_t(row) * args.out_cols + out_col0;

@@ -412,7 +412,7 @@ grouped_gemm_fp8_cols_kernel(const __grid_constant__ CUtensorMap map_w,
               float amax = fmaxf(fmaxf(tail->col_amax[par][0][col], tail->col_amax[par][1][col]),
                                  fmaxf(tail->col_amax[par][2][col], tail->col_amax[par][3][col]));
               amax = fmaxf(amax, 1e-10f);
-              const float scale = __fdiv_rn(amax, 448.0f);
+              const float scale = fp8_group_scale(amax, args.ue8m0);
               if (col < tc.valid) {
                 const float q = fminf(fmaxf(__fdiv_rn(acc0[m * 16 + j], scale), -448.f), 448.f);
                 if (feature < args.out_cols) out[size_t(tc.row0 + col) * args.out_cols + feature] = to_e4m3(q);

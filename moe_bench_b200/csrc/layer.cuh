@@ -44,7 +44,10 @@ int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, 
                         int hidden, __nv_bfloat16* out, cudaStream_t stream, int fp16 = 0);
 // Per-row, per-128-group e4m3 quantisation.  scales_t is [K/128][scale_ld] (group-major).
 int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uint8_t* q,
-                           float* scales, int64_t scale_ld, int transposed, cudaStream_t stream);
+                           float* scales, int64_t scale_ld, int transposed, cudaStream_t stream, int ue8m0 = 0);
+// Activation scale format the calling thread selected (mb200_set_fp8_scale_format): 0 = fp32
+// amax/448, 1 = rounded up to a power of two.
+int fp8_scale_ue8m0();
 
 // ---- grouped_gemm.cu -----------------------------------------------------------------
 struct GemmArgs {
@@ -134,6 +137,7 @@ struct GemmFp8Args {
   const float* row_scale;     // down: combine weights
   int* status;
   unsigned long long* clock_probe;  // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel
+  int ue8m0;                  // gate/up: re-quantise the activations with power-of-two scales
 };
 // Dispatch fused into the fp8 gate/up GEMM (128-row-tile kernel): two helper warps of every CTA
 // fill the sorted row buffer with the tokens' e4m3 rows and their 1x128 scales, 16-row granule by

@@ -406,7 +406,8 @@ extern "C" int mb200_align_noalloc(const int32_t* topk_ids, int64_t tokens, int 
                 "align_noalloc: %d local experts exceed the built-in scratch (at most %d); "
                 "use mb200_align with a caller-provided scratch buffer",
                 local_experts, kNoAllocMaxExperts);
-  const int64_t assignments = tokens * topk;
+  // compared before multiplying: tokens * topk must not wrap around on its way to the limit check
+  const int64_t assignments = tokens <= kNoAllocMaxAssignments / topk ? tokens * topk : kNoAllocMaxAssignments + 1;
   MB200_REQUIRE(assignments <= kNoAllocMaxAssignments, kUnsupportedShape,
                 "align_noalloc: %lld assignments exceed the built-in scratch (at most %lld); "
                 "use mb200_align with a caller-provided scratch buffer",

@@ -43,7 +43,7 @@ __global__ void combine_bf16_kernel(const uint4* __restrict__ y, const int* __re
 
 // Quantise the 16 elements a thread holds of a 128-wide group shared by 8
 // consecutive lanes; returns the group's scale (identical in the 8 lanes).
-__device__ __forceinline__ float quantize_slice16(const uint4& a, const uint4& b, uint32_t (&w)[4]) {
+__device__ __forceinline__ float quantize_slice16(const uint4& a, const uint4& b, uint32_t (&w)[4], int ue8m0) {
   float f[16];
   const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
   const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
@@ -59,7 +59,7 @@ __device__ __forceinline__ float quantize_slice16(const uint4& a, const uint4& b
 #pragma unroll
   for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, o));
   amax = fmaxf(amax, 1e-10f);
-  const float scale = __fdiv_rn(amax, 448.0f);
+  const float scale = fp8_group_scale(amax, ue8m0);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     uint32_t packed = 0;
@@ -76,14 +76,14 @@ __device__ __forceinline__ float quantize_slice16(const uint4& a, const uint4& b
 // One 128-wide group per 8 lanes (16 bf16 each).
 __global__ void group_quant_fp8_kernel(const uint4* __restrict__ x, int64_t rows, int groups_per_row,
                                        uint2* __restrict__ q, float* __restrict__ scales,
-                                       int64_t scale_ld, int transposed) {
+                                       int64_t scale_ld, int transposed, int ue8m0) {
   const int64_t total_groups = rows * groups_per_row;
   const int sub = threadIdx.x & 7;
   for (int64_t g = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3; g < total_groups;
        g += (int64_t(gridDim.x) * blockDim.x) >> 3) {
     const uint4* src = x + g * 16 + sub * 2;  // 16 elements = two 16-byte loads
     uint32_t w[4];
-    const float scale = quantize_slice16(__ldg(src), __ldg(src + 1), w);
+    const float scale = quantize_slice16(__ldg(src), __ldg(src + 1), w, ue8m0);
     uint2* dst = q + g * 16 + sub * 2;
     dst[0] = make_uint2(w[0], w[1]);
     dst[1] = make_uint2(w[2], w[3]);
@@ -124,14 +124,14 @@ int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, 
 }
 
 int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uint8_t* q, float* scales,
-                           int64_t scale_ld, int transposed, cudaStream_t stream) {
+                           int64_t scale_ld, int transposed, cudaStream_t stream, int ue8m0) {
   MB200_REQUIRE(hidden % 128 == 0, kUnsupportedShape, "group_quant: hidden=%d must be a multiple of 128", hidden);
   if (rows == 0) return kOk;
   const int threads = 256;
   const int blocks = grid_for(rows * (hidden / 128) * 8, threads, sm_count(), 16);
   group_quant_fp8_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(x), rows,
                                                         hidden / 128, reinterpret_cast<uint2*>(q), scales,
-                                                        scale_ld, transposed);
+                                                        scale_ld, transposed, ue8m0);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -44,6 +44,10 @@ class B200FusedExperts(MoEImplementation):
 
     name = "b200"
 
+    # fp8 activation scale format: None = what the reference does on this box (asked of vLLM
+    # in setup()), or "fp32" / "ue8m0" to fix it
+    fp8_scale_format = None
+
     def __init__(self) -> None:
         self._key = None
         self._workspace = None
@@ -80,6 +84,7 @@ class B200FusedExperts(MoEImplementation):
             # plugin-owned contiguous fp32 copies of the (small) scale tables
             self._w1_scale = qc.w1_scale.to(torch.float32).contiguous()
             self._w2_scale = qc.w2_scale.to(torch.float32).contiguous()
+            self._scale_format = self.fp8_scale_format or capi.reference_fp8_scale_format()
         capi.load()
         t, hidden = problem.hidden_states.shape
         e_local, two_n, _ = problem.w1.shape
@@ -102,6 +107,7 @@ class B200FusedExperts(MoEImplementation):
             raise capi.MB200Error("run() called with a problem of another shape than setup()")
         expert_map = problem.expert_map
         if self._fp8:
+            capi.set_fp8_scale_format(self._scale_format)
             capi.moe_forward_fp8(
                 problem.hidden_states, problem.w1, problem.w2, self._w1_scale, self._w2_scale,
                 problem.topk_ids, problem.topk_weights, expert_map, self._out, self._workspace,

@@ -151,6 +151,10 @@ class B200Scheme(DistributedScheme):
 
     name = "b200"
 
+    # fp8 activation scale format: None = what the reference does on this box (asked of vLLM
+    # in setup()), or "fp32" / "ue8m0" to fix it
+    fp8_scale_format = None
+
     def __init__(self) -> None:
         self._buf = None
         self._seq = 0
@@ -176,6 +180,7 @@ class B200Scheme(DistributedScheme):
                 raise capi.MB200Error("fp8 needs quant_config with block_shape [128, 128]")
             self._w1_scale = qc.w1_scale.to(torch.float32).contiguous()
             self._w2_scale = qc.w2_scale.to(torch.float32).contiguous()
+            self._scale_format = self.fp8_scale_format or capi.reference_fp8_scale_format()
         if self._ep and problem.expert_map is None:
             raise capi.MB200Error("expert-parallel problem without expert_map")
         t, hidden = problem.hidden_states.shape
@@ -200,6 +205,8 @@ class B200Scheme(DistributedScheme):
 
     def run(self) -> torch.Tensor:
         p = self.problem
+        if self._fp8:
+            capi.set_fp8_scale_format(self._scale_format)
         capi.dist_forward(
             self._precision, self._ep, self._hidden, p.w1, p.w2, self._w1_scale, self._w2_scale, self._ids,
             self._weights, p.expert_map if self._ep else None, self._out, p.config.num_experts, self.ctx.rank,

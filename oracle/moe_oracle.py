@@ -40,6 +40,12 @@ import torch.nn.functional as F
 FP8 = torch.float8_e4m3fn
 FP8_MAX = 448.0
 
+# Format of the fp8 activation scales: "fp32" (amax/448) or "ue8m0" (rounded up to a power of
+# two).  The reference leaves the choice to vLLM, which uses the second on GPUs where its
+# DeepGEMM path is enabled (Hopper, Blackwell) and the first elsewhere; callers that check a
+# GPU run set this to what the library was told to compute.
+FP8_SCALE_FORMAT = "fp32"
+
 # (atol, rtol) per precision: reference.py:39-43.
 DEFAULT_TOL = {"bf16": (2e-2, 0.0), "fp16": (1e-2, 0.0), "fp8": (3.5e-2, 3.5e-2)}
 
@@ -106,7 +112,7 @@ def route_topk(logits: torch.Tensor, k: int):
 # ----------------------------------------------------------------------------
 # fp8 quantisation
 # ----------------------------------------------------------------------------
-def group_quant_fp8(x: torch.Tensor, group: int = 128, eps: float = 1e-10):
+def group_quant_fp8(x: torch.Tensor, group: int = 128, eps: float = 1e-10, scale_format: str | None = None):
     """Per-row, per-``group`` dynamic e4m3 quantisation of activations.
 
     Semantics of vLLM 0.22.0 ``per_token_group_quant_fp8`` as the reference
@@ -115,14 +121,19 @@ def group_quant_fp8(x: torch.Tensor, group: int = 128, eps: float = 1e-10):
     ``scale = amax / 448`` (an IEEE division; vLLM's Triton fallback multiplies
     by the reciprocal instead, which differs in the last bit for ~60 % of the
     groups), ``q = clamp(x / scale, -448, 448)`` rounded to nearest-even e4m3.
+    With ``scale_format="ue8m0"`` (default: the module's ``FP8_SCALE_FORMAT``) the
+    scale is then rounded up to a power of two, ``exp2(ceil(log2(scale)))``, as
+    vLLM does when it runs with DeepGEMM's E8M0 scales.
     The GPU test-suite compares the CUDA kernel of this package with vLLM's op
-    byte for byte where vLLM is installed.
+    byte for byte, in both formats, where vLLM is installed.
     Returns ``(q (m, K) e4m3, scales (m, K/group) fp32)``.
     """
     m, k = x.shape
     xf = x.float().view(m, k // group, group)
     amax = xf.abs().amax(dim=-1, keepdim=True).clamp_min(eps)
     scale = amax / np.float32(FP8_MAX)
+    if (scale_format or FP8_SCALE_FORMAT) == "ue8m0":
+        scale = torch.exp2(torch.ceil(torch.log2(scale.abs().clamp_min(1e-10))))
     q = (xf / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
     return q.view(m, k), scale.view(m, k // group)
 

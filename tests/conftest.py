@@ -32,3 +32,21 @@ def golden():
     import torch
 
     return torch.load(GOLDEN, weights_only=False)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _fp8_scale_format_of_this_box():
+    """On a GPU box the library quantises activations the way the reference does THERE (vLLM
+    uses power-of-two scales where its DeepGEMM path is enabled); the oracle and the library's
+    direct calls from the test thread follow.  Without a GPU: the plain fp32 format."""
+    import torch
+
+    if not torch.cuda.is_available():
+        yield "fp32"
+        return
+    from moe_bench_b200 import capi
+    from oracle import moe_oracle as O
+
+    O.FP8_SCALE_FORMAT = capi.use_reference_fp8_scale_format()
+    yield O.FP8_SCALE_FORMAT
+    O.FP8_SCALE_FORMAT = "fp32"

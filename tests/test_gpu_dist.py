@@ -65,10 +65,12 @@ def _rank_main(rank, world, port, mode, precision, tokens, dist_name, q):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
+    from moe_bench_b200 import capi
     from moe_bench_b200.scheme import DistContext, get_scheme
 
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
+    O.FP8_SCALE_FORMAT = capi.use_reference_fp8_scale_format()  # the oracle follows the library on this box
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("cpu:gloo,cuda:nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank,
                             world_size=world, device_id=dev)

@@ -122,10 +122,12 @@ def test_fp8_layer_matches_reference_outputs(golden, name, rank):
     cfg = P.MoEBenchConfig.from_dict(case["config"])
     prob = P.make_problem(cfg, case["num_tokens"], rank)
     impl = get_implementation("b200")
+    impl.fp8_scale_format = "fp32"   # the fixtures were made with the plain fp32 activation scales
     dprob = _to_dev(prob)
     impl.setup(dprob)
     out = impl.run(dprob)
     assert impl.device_status() == 0
+    capi.use_reference_fp8_scale_format()
     _check(out, case["reference"])
 
 
@@ -168,20 +170,56 @@ def test_fp8_dsv32_shape_sampled_tokens():
     assert res.passed and res.rel_err < 1e-3, (res.message, res.rel_err)
 
 
-def test_group_quant_matches_vllm_op_if_present():
+@pytest.mark.parametrize("fmt", ["fp32", "ue8m0"])
+def test_group_quant_matches_vllm_op_if_present(fmt):
     """The activation quantiser the reference calls on a GPU is vLLM's
-    per_token_group_quant_fp8; where vLLM is installed, compare byte for byte."""
+    per_token_group_quant_fp8; where vLLM is installed, compare byte for byte, in both
+    scale formats (which one the reference gets depends on the box: vLLM picks
+    power-of-two scales where its DeepGEMM path is enabled)."""
     try:
         from vllm.model_executor.layers.quantization.utils.fp8_utils import per_token_group_quant_fp8
     except Exception as exc:  # noqa: BLE001
         pytest.skip(f"vLLM not importable: {exc}")
     x = (torch.randn(257, 7168, generator=torch.Generator().manual_seed(4)) * 2).to(torch.bfloat16).to(DEV)
     try:
-        vq, vs = per_token_group_quant_fp8(x, 128, use_ue8m0=False)
+        vq, vs = per_token_group_quant_fp8(x, 128, use_ue8m0=(fmt == "ue8m0"))
     except Exception as exc:  # noqa: BLE001
         pytest.skip(f"vLLM quantiser not runnable here: {exc}")
-    q, s = capi.group_quant_fp8(x)
+    capi.set_fp8_scale_format(fmt)
+    try:
+        q, s = capi.group_quant_fp8(x)
+    finally:
+        capi.use_reference_fp8_scale_format()
     same_scale = float((s == vs.reshape(s.shape)).float().mean())
     same_bytes = float((q.view(torch.uint8) == vq.view(torch.uint8)).float().mean())
-    print(f"vLLM quantiser agreement: scales {same_scale:.6f}, bytes {same_bytes:.6f}")
+    print(f"vLLM quantiser agreement ({fmt}): scales {same_scale:.6f}, bytes {same_bytes:.6f}")
     assert same_scale == 1.0 and same_bytes == 1.0
+    # and the CPU oracle's quantiser in the same format
+    oq, os_ = O.group_quant_fp8(x.cpu(), scale_format=fmt)
+    assert torch.equal(oq.view(torch.uint8), q.cpu().view(torch.uint8)) and torch.equal(os_, s.cpu())
+
+
+@pytest.mark.parametrize("fmt", ["fp32", "ue8m0"])
+def test_layer_in_both_activation_scale_formats(fmt):
+    """The whole fp8 layer in each scale format (whichever the box's vLLM picks, both are
+    exercised), against the oracle computing in the same format."""
+    from moe_bench_b200.plugin import get_implementation
+
+    cfg = P.MoEBenchConfig(hidden_size=512, intermediate_size=256, num_experts=8, topk=2, world_size=1,
+                           precision=P.Precision.FP8, seed=0, device=DEV)
+    for tokens in (5, 700):   # tokens-on-columns kernels, 128-row-tile kernels
+        prob = P.make_problem(cfg, tokens)
+        impl = get_implementation("b200")
+        impl.fp8_scale_format = fmt
+        impl.setup(prob)
+        out = impl.run(prob)
+        assert impl.device_status() == 0
+        before = O.FP8_SCALE_FORMAT
+        O.FP8_SCALE_FORMAT = fmt
+        try:
+            ref = O.reference_moe(prob)
+        finally:
+            O.FP8_SCALE_FORMAT = before
+        res = O.verify_output("fp8", out, ref)
+        assert res.passed and res.rel_err < 1e-2, (tokens, res.message, res.rel_err)
+    capi.use_reference_fp8_scale_format()

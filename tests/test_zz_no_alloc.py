@@ -14,11 +14,13 @@ The file name makes pytest collect it last: a run that stops at the first
 failure has then already executed every other test.
 """
 
+import numpy as np
 import pytest
 import torch
 
 from moe_bench_b200 import capi
 from moe_bench_b200 import problem as P
+from oracle import moe_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -79,6 +81,12 @@ def test_noalloc_align_matches_align_on_consecutive_calls():
         assert torch.cuda.mem_get_info()[0] >= free_before
         _same(got, want)
         _same(got_again, want)
+        # and against the CPU oracle directly, not only through the other entry point
+        o_counts, o_off, o_sorted, o_inv = O.align(ids.cpu().numpy(), None if emap is None else emap.cpu().numpy(),
+                                                   local, pad)
+        assert np.array_equal(got[0].cpu().numpy(), o_counts) and np.array_equal(got[1].cpu().numpy() * pad, o_off)
+        used = int(o_off[-1])
+        assert np.array_equal(got[2].cpu().numpy()[:used], o_sorted) and np.array_equal(got[3].cpu().numpy(), o_inv)
         # drop this iteration's tensors now, so the next iteration's measurement sees no frees
         del got, got_again, want, outs, outs2
 
