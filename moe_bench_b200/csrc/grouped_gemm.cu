@@ -19,7 +19,7 @@
 // baseline.py:62-76 and the ThunderKittens grouped GEMM of
 // kernels/tileoverlap/common/sm120_common.cuh:149-274).
 //
-// One persistent CTA per SM, 448 threads: warp 0 issues TMA loads into a ring of
+// One persistent CTA per SM, 512 threads: warp 0 issues TMA loads into a ring of
 // 128-byte-swizzled stages (32 KiB of weights + exactly the tile's token rows, one
 // TMA box per set bit of ntok/16), warp 1 owns tensor memory and issues tcgen05.mma,
 // warps 2-9 drain the accumulators: tcgen05.ld of two 16-token chunks per round
@@ -32,7 +32,8 @@
 // the TMA warp starts a tile only when all granules of its token block have
 // arrived (acquire on the counters, then a proxy fence).  Dispatch warps never
 // wait, so a cooperative launch (all CTAs resident) makes the scheme deadlock-free.
-// In the down GEMM, which has no dispatch, warps 10-13 drain accumulators too.
+// In the down GEMM, which has no dispatch, warps 10-13 drain accumulators too; expert
+// parallel, its warps 14-15 push finished rows to the GPUs that own the tokens.
 // The token box (16/32/64/128/256 rows), the stage size, the number of stages and
 // whether the accumulators are double-buffered (token box <= 128) are derived on
 // the device from the largest expert segment in the schedule, so one launch suits
@@ -55,7 +56,9 @@ constexpr int kFirstEpilogueWarp = 2;
 constexpr int kDispatchWarps = kDispatchWarpsPerCta;  // warps 10-13: fused dispatch (gate/up GEMM only)
 constexpr int kDispatchLoads = 14;  // 16-byte loads each dispatch lane keeps in flight
 constexpr int kFirstDispatchWarp = kFirstEpilogueWarp + kEpilogueWarps;
-constexpr int kThreads = (kFirstDispatchWarp + kDispatchWarps) * 32;
+constexpr int kPushWarps = 2;       // warps 14-15: fused combine push (down GEMM, expert parallel)
+constexpr int kFirstPushWarp = kFirstDispatchWarp + kDispatchWarps;
+constexpr int kThreads = (kFirstPushWarp + kPushWarps) * 32;
 constexpr int kMaxTokens = 256;
 
 struct SmemTail {
@@ -155,8 +158,8 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-// kPush (down GEMM, expert parallel): warps 10-13 forward finished rows to the GPUs that own
-// the tokens instead of draining accumulators.
+// kPush (down GEMM, expert parallel): warps 14-15 forward finished rows to the GPUs that own
+// the tokens (they idle otherwise).
 template <int kMode, bool kPush>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -173,7 +176,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
   const int lane = threadIdx.x & 31;
   const int E = args.num_experts;
   // the down GEMM has no dispatch: its warps 10-13 drain accumulators too
-  constexpr int kEpiWarps = (kMode == kDownWeighted && !kPush) ? kEpilogueWarps + kDispatchWarps : kEpilogueWarps;
+  constexpr int kEpiWarps = kMode == kDownWeighted ? kEpilogueWarps + kDispatchWarps : kEpilogueWarps;
   constexpr int kChunkStride = kEpiWarps / 4;  // warps per tensor-memory lane quarter
   const int worker = int(blockIdx.x);
   const int workers = int(gridDim.x);
@@ -358,6 +361,8 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
       if (ok && lane == 0) tc_commit(smem_u32(&tail->acc_full[buf]));
       __syncwarp();
     }
+  } else if (warp >= kFirstPushWarp && !(kMode == kDownWeighted && kPush)) {
+    // warps 14-15 have no work in this kernel variant
   } else if (kMode == kGateUpSwiglu && warp >= kFirstDispatchWarp) {
     // ---------------- fused dispatch (gate/up GEMM): fill the sorted row buffer ----------------
     if (kMode == kGateUpSwiglu && disp.enabled == kDispatchFused) {
@@ -393,14 +398,14 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
         if (lane == 0) atomicAdd(disp.granule_done + g, 1);
       }
     }
-  } else if (kMode == kDownWeighted && kPush && warp >= kFirstDispatchWarp) {
+  } else if (kMode == kDownWeighted && kPush && warp >= kFirstPushWarp) {
     // ---------------- fused combine push (down GEMM, expert parallel) ----------------
     // Work unit = one 16-row granule of the sorted rows, granules strided over the CTAs in row
     // order (= the order in which the tiles finish).  A granule is forwarded once every feature
     // block of its token block has been stored by the epilogue warps of whichever CTAs computed
     // them.  The GEMM warps never wait for these warps, so with all CTAs resident (cooperative
     // launch) the wait cannot deadlock; it is bounded like every other wait.
-    const int pw = warp - kFirstDispatchWarp;
+    const int pw = warp - kFirstPushWarp;
     const int granules = tail->prefix[E];
     const int target = args.n_tiles * kEpiWarps;
     bool ok = true;
@@ -432,7 +437,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w,
         __nanosleep(256);
       }
       if (!ok) break;
-      for (int i = pw; i < kPad; i += kDispatchWarps) {
+      for (int i = pw; i < kPad; i += kPushWarps) {
         const int n = __ldg(args.sorted_ids + g * kPad + i);
         if (n >= push.own_rows) {  // a token of another rank (own tokens were stored in place; -1 = padding)
           const int tok_global = n / push.topk;

@@ -102,7 +102,9 @@ constexpr int kFusedWarps = 32;
 __host__ __device__ inline int64_t unit_chunk(int64_t assignments, int units_cap) {
   int64_t chunk = (assignments + units_cap - 1) / units_cap;
   chunk = (chunk + 31) / 32 * 32;
-  return chunk < 1024 ? 1024 : chunk;
+  // a warp walks its unit 32 assignments at a time, one dependent load per step: short units
+  // (more warps in flight) keep the walk from being a chain of load latencies
+  return chunk < 256 ? 256 : chunk;
 }
 
 __device__ __forceinline__ int slot_of(const int* topk_ids, const int* expert_map, int64_t n,
