@@ -732,8 +732,9 @@ def _nvlink_report(leg: Leg, disp: dict, stage_ms) -> dict:
         d_bytes = (env.world - 1) * leg.tokens * row_bytes
         d_ms, d_note = names["dispatch"], "token blocks of all peers pulled once, before the GEMM"
         c_bytes = leg.tokens * (env.world - 1) * HIDDEN * 2
-        c_ms, c_note = names["combine"], ("one pre-reduced row per own token from every peer, pulled and summed; "
-                                          "the stage includes its barriers")
+        c_ms, c_note = names["combine"], ("one row per own token from every peer (its sum over the token's k "
+                                          "assignments), pushed by the peer; the stage = that kernel, the "
+                                          "barrier and the sum of the W planes")
     else:
         owner = (leg.ids // leg.e_local).long()
         remote_assign = int((owner != env.rank).sum().item())
@@ -1117,10 +1118,9 @@ def _dist_kernels_per_step(n_align: int, fp8: bool, tp: bool, fused: bool) -> in
     gather], [TP: block gathers], two GEMMs, local pre-reduce, partial reduce."""
     if not tp and fused:
         return n_align + 2 + 1 + 2 + 1 + (1 if fp8 else 0)
-    n = n_align + 3 + 5 + (2 if fp8 else 0)
-    if tp:
-        n += 2 if fp8 else 1
-    return n
+    if tp:  # 2 barriers, routing gather, align, [quantise], block gather(s), [row gather], 2 GEMMs, sum+push, plane sum
+        return n_align + 2 + 1 + (1 if fp8 else 0) + (2 if fp8 else 1) + (0 if fused else 1) + 2 + 2
+    return n_align + 3 + 5 + 2   # fp8 with few rows per expert: separate gather, pre-reduce and pull
 
 
 def _decompose(leg: Leg, ms_fused: float, stage_ms, steps: int, warmup: int) -> dict:

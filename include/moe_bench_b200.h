@@ -244,9 +244,11 @@ int mb200_moe_forward_fp8(const void* hidden_states, const void* w1, const void*
  * One forward = stage own tokens and routing | barrier | routing of all ranks,
  * sort-and-pad | gate/up GEMM whose helper warps pull the rows it needs over
  * NVLink | down GEMM whose helper warps push finished rows to the tokens' owners
- * | barrier | sum of the k rows of every own token.  (Tensor parallel, and fp8
- * with at most 24 rows per expert: token blocks / rows are gathered before the
- * GEMM and pre-reduced partial rows are pulled after a barrier, three barriers.)
+ * | barrier | sum of the k rows of every own token.  (Tensor parallel: peers'
+ * token blocks are gathered before the GEMM and each rank pushes the sum over a
+ * token's k rows to the owner, who sums W planes; two barriers.  fp8 with at
+ * most 24 rows per expert: rows gathered before the GEMM, pre-reduced partial
+ * rows pulled after a barrier; three barriers.)
  * seq_base: a counter that is equal on all ranks and grows by
  * MB200_DIST_SEQ_STRIDE per call (barrier sequence numbers are never reset).
  * All ranks must make the same calls in the same order.  A barrier that does not

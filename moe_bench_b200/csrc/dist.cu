@@ -293,13 +293,23 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
     if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 2, status, s))) return rc;
     rc = launch_combine_bf16(reinterpret_cast<const __nv_bfloat16*>(sym + sl.yrecv), nullptr, int(tokens), topk,
                              hidden, reinterpret_cast<__nv_bfloat16*>(out), s, fp16);
+  } else if (!expert_parallel) {
+    // Tensor parallel: every rank holds a partial result for EVERY token.  The sum over a token's
+    // k rows goes straight into the owner's `partial` plane of this rank (16-byte stores over
+    // NVLink while the k-fold rows stream from HBM); after the barrier the owner sums its W
+    // local planes.  Two barriers per forward, for the reasons given above.
+    if ((rc = launch_combine_push(y, int(all_tokens), int(tokens), topk, hidden,
+                                  offset_table(symmetric_ptrs, world, sl.partial), rank, world, s, fp16))) return rc;
+    if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 2, status, s))) return rc;
+    rc = launch_sum_planes(reinterpret_cast<const __nv_bfloat16*>(sym + sl.partial), int(tokens), world, hidden,
+                           reinterpret_cast<__nv_bfloat16*>(out), s, fp16);
   } else {
     if ((rc = launch_combine_bf16(y, sched.inverse, int(all_tokens), topk, hidden,
                                   reinterpret_cast<__nv_bfloat16*>(sym + sl.partial), s, fp16))) return rc;
     // 5. combine across ranks
     if ((rc = launch_peer_barrier(flags, rank, world, seq_base + 2, status, s))) return rc;
     if ((rc = launch_reduce_partials(offset_table(symmetric_ptrs, world, sl.partial), rank, world, int(tokens), topk,
-                                     topk_ids, expert_parallel ? local_experts : 0, hidden,
+                                     topk_ids, local_experts, hidden,
                                      reinterpret_cast<__nv_bfloat16*>(out), s, fp16))) return rc;
     // peers may still be reading this rank's buffers: nobody restages before all are done
     rc = launch_peer_barrier(flags, rank, world, seq_base + 3, status, s);

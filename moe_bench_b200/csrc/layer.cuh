@@ -42,6 +42,12 @@ int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map
 // y and out are 16-bit (bf16, or fp16 when fp16 != 0); fp32 sum.
 int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, int topk,
                         int hidden, __nv_bfloat16* out, cudaStream_t stream, int fp16 = 0);
+// Tensor parallel combine: sum over k and store the row into the owner's `partial` plane of this
+// rank; then the owner's sum over its W local planes.
+int launch_combine_push(const __nv_bfloat16* y, int all_tokens, int tokens_per_rank, int topk, int hidden,
+                        const PeerTable& partial, int rank, int world, cudaStream_t stream, int fp16 = 0);
+int launch_sum_planes(const __nv_bfloat16* partial, int tokens, int world, int hidden, __nv_bfloat16* out,
+                      cudaStream_t stream, int fp16 = 0);
 // Per-row, per-128-group e4m3 quantisation.  scales_t is [K/128][scale_ld] (group-major).
 int launch_group_quant_fp8(const __nv_bfloat16* x, int64_t rows, int hidden, uint8_t* q,
                            float* scales, int64_t scale_ld, int transposed, cudaStream_t stream, int ue8m0 = 0);

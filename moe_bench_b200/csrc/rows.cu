@@ -41,6 +41,57 @@ __global__ void combine_bf16_kernel(const uint4* __restrict__ y, const int* __re
   }
 }
 
+// Tensor parallel: the same sum over a token's k rows, but the result goes straight to the rank
+// that owns the token, into the plane of its `partial` buffer that belongs to this rank
+// (row i of y's token space is token t = i mod T of rank (rank + i / T) mod W), as 16-byte
+// stores over NVLink.  Replaces "sum locally, barrier, owner pulls": the owner then sums W
+// local planes.
+__global__ void combine_push_kernel(const uint4* __restrict__ y, int all_tokens, int tokens_per_rank, int topk,
+                                    int vec_per_row, PeerTable partial, int rank, int world, int fp16) {
+  const int64_t total = int64_t(all_tokens) * vec_per_row;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t row = i / vec_per_row;
+    const int v = int(i - row * vec_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j0 = 0; j0 < topk; j0 += 8) {
+      uint4 val[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (j0 + u < topk) val[u] = __ldg(y + (row * topk + j0 + u) * vec_per_row + v);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (j0 + u < topk) add_h16x8(val[u], acc, fp16);
+    }
+    const int ring = int(row / tokens_per_rank);
+    const int t = int(row - int64_t(ring) * tokens_per_rank);
+    uint4* dst = reinterpret_cast<uint4*>(partial.ptr[(rank + ring) % world]) +
+                 (int64_t(rank) * tokens_per_rank + t) * vec_per_row + v;
+    *dst = pack_h16x8(acc, fp16);
+  }
+  __threadfence_system();  // the stores to the peers are performed before the kernel ends
+}
+
+// out[t] = sum over the W planes of this rank's own `partial` buffer, ascending plane.
+__global__ void sum_planes_kernel(const uint4* __restrict__ partial, int tokens, int world, int vec_per_row,
+                                  uint4* __restrict__ out, int fp16) {
+  const int64_t total = int64_t(tokens) * vec_per_row;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p0 = 0; p0 < world; p0 += 8) {
+      uint4 val[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (p0 + u < world) val[u] = __ldg(partial + int64_t(p0 + u) * total + i);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (p0 + u < world) add_h16x8(val[u], acc, fp16);
+    }
+    out[i] = pack_h16x8(acc, fp16);
+  }
+}
+
 // Quantise the 16 elements a thread holds of a 128-wide group shared by 8
 // consecutive lanes; returns the group's scale (identical in the 8 lanes).
 __device__ __forceinline__ float quantize_slice16(const uint4& a, const uint4& b, uint32_t (&w)[4], int ue8m0) {
@@ -119,6 +170,27 @@ int launch_combine_bf16(const __nv_bfloat16* y, const int* inverse, int tokens, 
   const int blocks = grid_for(int64_t(tokens) * (hidden / 8), threads, sm_count(), 16);
   combine_bf16_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(y), inverse, tokens,
                                                      topk, hidden / 8, reinterpret_cast<uint4*>(out), fp16);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_combine_push(const __nv_bfloat16* y, int all_tokens, int tokens_per_rank, int topk, int hidden,
+                        const PeerTable& partial, int rank, int world, cudaStream_t stream, int fp16) {
+  MB200_REQUIRE(hidden % 8 == 0, kUnsupportedShape, "combine: hidden=%d must be a multiple of 8", hidden);
+  const int threads = 256;
+  const int blocks = grid_for(int64_t(all_tokens) * (hidden / 8), threads, sm_count(), 16);
+  combine_push_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(y), all_tokens, tokens_per_rank,
+                                                     topk, hidden / 8, partial, rank, world, fp16);
+  MB200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int launch_sum_planes(const __nv_bfloat16* partial, int tokens, int world, int hidden, __nv_bfloat16* out,
+                      cudaStream_t stream, int fp16) {
+  const int threads = 256;
+  const int blocks = grid_for(int64_t(tokens) * (hidden / 8), threads, sm_count(), 16);
+  sum_planes_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint4*>(partial), tokens, world, hidden / 8,
+                                                   reinterpret_cast<uint4*>(out), fp16);
   MB200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
