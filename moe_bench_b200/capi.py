@@ -146,6 +146,26 @@ def _need(t: torch.Tensor, dtype, name: str) -> None:
         raise MB200Error(f"{name}: need a contiguous CUDA tensor of {dtype}, got {t.dtype} on {t.device}")
 
 
+def check_problem_tensors(problem, dtype) -> None:
+    """The layer entry points take raw pointers: refuse tensors of another dtype, device or
+    layout here instead of computing on garbage (called from ``setup()``, not in the timed path)."""
+    _need(problem.hidden_states, dtype, "hidden_states")
+    _need(problem.topk_ids, torch.int32, "topk_ids")
+    _need(problem.topk_weights, torch.float32, "topk_weights")
+    for name in ("w1", "w2"):
+        w = getattr(problem, name)
+        if not w.is_cuda or not w.is_contiguous():
+            raise MB200Error(f"{name}: need a contiguous CUDA tensor")
+    if problem.w1.dtype != problem.w2.dtype:
+        raise MB200Error(f"w1 is {problem.w1.dtype} but w2 is {problem.w2.dtype}")
+    if problem.expert_map is not None:
+        _need(problem.expert_map, torch.int32, "expert_map")
+        if problem.topk_ids.numel() and int(problem.topk_ids.max()) >= problem.expert_map.numel():
+            raise MB200Error("topk_ids holds an expert id beyond the end of expert_map")
+    if problem.topk_ids.numel() and int(problem.topk_ids.min()) < 0:
+        raise MB200Error("topk_ids holds a negative expert id")
+
+
 def row_capacity(tokens: int, topk: int, local_experts: int, pad_rows: int = PAD_ROWS_BF16) -> int:
     return int(load().mb200_row_capacity(tokens, topk, local_experts, pad_rows))
 

@@ -86,6 +86,7 @@ class B200FusedExperts(MoEImplementation):
             self._w2_scale = qc.w2_scale.to(torch.float32).contiguous()
             self._scale_format = self.fp8_scale_format or capi.reference_fp8_scale_format()
         capi.load()
+        capi.check_problem_tensors(problem, self._dtype)
         t, hidden = problem.hidden_states.shape
         e_local, two_n, _ = problem.w1.shape
         topk = problem.topk_ids.shape[1]

@@ -183,6 +183,7 @@ class B200Scheme(DistributedScheme):
             self._scale_format = self.fp8_scale_format or capi.reference_fp8_scale_format()
         if self._ep and problem.expert_map is None:
             raise capi.MB200Error("expert-parallel problem without expert_map")
+        capi.check_problem_tensors(problem, self._dtype)
         t, hidden = problem.hidden_states.shape
         e_local, two_n, _ = problem.w1.shape
         topk = problem.topk_ids.shape[1]
