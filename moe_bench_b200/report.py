@@ -21,6 +21,7 @@ _COLUMNS = [
     ("num_tokens", "tokens", "{:>7d}"),
     ("precision", "prec", "{:>5s}"),
     ("n_gpus", "gpus", "{:>4d}"),
+    ("mode", "mode", "{:>6s}"),
     ("latency_us", "latency(us)", "{:>12.1f}"),
     ("tflops", "TFLOP/s", "{:>9.1f}"),
     ("roofline_frac", "of roofline", "{:>11.2f}"),
@@ -71,6 +72,38 @@ def rows_from_bench(line: Dict[str, Any]) -> Dict[str, Any]:
     return row
 
 
+def rows_from_secondary(line: Dict[str, Any]) -> List[Dict[str, Any]]:
+    """Rows for the other sweep points a bench line carries under ``secondary``.
+
+    The reference's sweep prints one row per token count (``bench.py:52-118``); a
+    ``bench.py`` line of this repository holds the headline point at the top level
+    and the remaining points (other token counts, fp8, tensor parallel) as a list.
+    """
+    cfg = line.get("config", {})
+    topk = int(cfg.get("topk", 0))
+    rows = []
+    for leg in line.get("secondary") or []:
+        if "ms" not in leg:
+            continue
+        tokens = int(leg.get("tokens_per_gpu", 0))
+        rows.append({
+            "num_tokens": tokens,
+            "latency_us": float(leg["ms"]) * 1e3,
+            "tflops": float(leg.get("tflops", 0.0)),
+            "local_assignments": tokens * topk,
+            "timing": "events",
+            "rel_err": leg.get("rel_err"),
+            "verify": leg.get("verify", "n/a"),
+            "precision": leg.get("precision", "?"),
+            "mode": leg.get("mode"),
+            "n_gpus": int(line.get("n_gpus", 1)),
+            "roofline_frac": leg.get("layer_roofline_frac"),
+            "stage_us": {k: v * 1e3 for k, v in (leg.get("stage_ms") or {}).items()},
+            "stage_achieved": {},
+        })
+    return rows
+
+
 def format_table(rows: Iterable[Dict[str, Any]]) -> str:
     rows = list(rows)
     cols = [c for c in _COLUMNS if any(r.get(c[0]) is not None for r in rows)]
@@ -111,10 +144,16 @@ def main(argv=None) -> None:
     ap.add_argument("--json", help="also write the reference-shaped payload here")
     args = ap.parse_args(argv)
     lines = [_load(p) for p in args.files]
-    rows = sorted((rows_from_bench(l) for l in lines), key=lambda r: (r["precision"], r["n_gpus"], r["num_tokens"]))
+    rows = [rows_from_bench(l) for l in lines]
+    headline = {id(r) for r in rows}
+    for l, head in zip(lines, list(rows)):
+        head["mode"] = (l.get("config") or {}).get("mode") or ("single" if head["n_gpus"] == 1 else None)
+        same = lambda r: (r["num_tokens"], r["precision"], r.get("mode")) == (head["num_tokens"], head["precision"], head["mode"])
+        rows.extend(r for r in rows_from_secondary(l) if not same(r))
+    rows.sort(key=lambda r: (r["precision"], r["n_gpus"], r.get("mode") or "", r["num_tokens"]))
     print(format_table(rows))
     for r in rows:
-        if r["stage_us"]:
+        if r["stage_us"] and id(r) in headline:
             print()
             print(stage_table(r))
     if args.json:

@@ -31,3 +31,18 @@ def test_table_renders(tmp_path, capsys):
     text = capsys.readouterr().out
     assert "TFLOP/s" in text and "gate_up_gemm" in text and "8192" in text
     assert json.load(open(out))["results"][0]["verify"] == "ok"
+
+
+def test_secondary_legs_become_rows():
+    line = json.load(open(SAMPLE))
+    line["secondary"] = [
+        {"precision": "fp8", "tokens_per_gpu": 128, "mode": "single", "ms": 1.8, "tflops": 50.0,
+         "layer_roofline_frac": 0.94, "verify": "ok", "rel_err": 2.3e-3, "stage_ms": {"gate_up_gemm": 1.1}},
+        {"precision": "fp8", "tokens_per_gpu": 1, "skipped": "time budget"},
+    ]
+    rows = R.rows_from_secondary(line)
+    assert len(rows) == 1                               # a skipped leg has no timing and makes no row
+    r = rows[0]
+    assert r["num_tokens"] == 128 and r["local_assignments"] == 128 * 8 and r["precision"] == "fp8"
+    assert abs(r["latency_us"] - 1800.0) < 1e-9 and r["verify"] == "ok" and r["stage_us"]["gate_up_gemm"] == 1100.0
+    assert "fp8" in R.format_table([R.rows_from_bench(line)] + rows)
