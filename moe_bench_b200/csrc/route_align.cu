@@ -159,24 +159,66 @@ __global__ void align_count_kernel(const int* __restrict__ topk_ids, const int* 
 }
 
 // One block.  unit_hist[u][e] becomes the exclusive prefix over units; counts and
-// the cumulative M-tile table are written.
+// the cumulative M-tile table are written.  With `part` ([warps][E] ints of shared
+// memory) every warp scans a contiguous range of units, lanes across experts, in
+// two passes (range sums, then the prefix from the sums of the warps before it);
+// without it one thread per expert walks all units.
 __device__ void scan_units_and_experts(int* unit_hist, int units, int local_experts, int* counts,
-                                       int* mtile_prefix, int* smem_tiles /*[E+1]*/, int pad) {
-  for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
-    int run = 0;
-    for (int u0 = 0; u0 < units; u0 += 8) {
-      int v[8];  // loads first, so eight of them are in flight together
+                                       int* mtile_prefix, int* smem_tiles /*[E+1]*/, int* part, int pad) {
+  if (part != nullptr) {
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_warp = (units + warps - 1) / warps;
+    const int u_lo = warp * per_warp < units ? warp * per_warp : units;
+    const int u_hi = u_lo + per_warp < units ? u_lo + per_warp : units;
+    for (int e = lane; e < local_experts; e += 32) {
+      int sum = 0;
+      for (int u0 = u_lo; u0 < u_hi; u0 += 8) {
+        int v[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        v[i] = (u0 + i < units) ? unit_hist[size_t(u0 + i) * local_experts + e] : 0;
+        for (int i = 0; i < 8; ++i)
+          v[i] = (u0 + i < u_hi) ? unit_hist[size_t(u0 + i) * local_experts + e] : 0;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (u0 + i < units) unit_hist[size_t(u0 + i) * local_experts + e] = run;
-        run += v[i];
+        for (int i = 0; i < 8; ++i) sum += v[i];
+      }
+      part[warp * local_experts + e] = sum;
+    }
+    __syncthreads();
+    for (int e = lane; e < local_experts; e += 32) {
+      int run = 0;
+      for (int w = 0; w < warp; ++w) run += part[w * local_experts + e];
+      for (int u0 = u_lo; u0 < u_hi; u0 += 8) {
+        int v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          v[i] = (u0 + i < u_hi) ? unit_hist[size_t(u0 + i) * local_experts + e] : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (u0 + i < u_hi) unit_hist[size_t(u0 + i) * local_experts + e] = run;
+          run += v[i];
+        }
+      }
+      if (warp == warps - 1) {  // the last warp's running sum is the expert's total
+        counts[e] = run;
+        smem_tiles[e] = (run + pad - 1) / pad;
       }
     }
-    counts[e] = run;
-    smem_tiles[e] = (run + pad - 1) / pad;
+  } else {
+    for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
+      int run = 0;
+      for (int u0 = 0; u0 < units; u0 += 8) {
+        int v[8];  // loads first, so eight of them are in flight together
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          v[i] = (u0 + i < units) ? unit_hist[size_t(u0 + i) * local_experts + e] : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (u0 + i < units) unit_hist[size_t(u0 + i) * local_experts + e] = run;
+          run += v[i];
+        }
+      }
+      counts[e] = run;
+      smem_tiles[e] = (run + pad - 1) / pad;
+    }
   }
   __syncthreads();
   if (threadIdx.x < 32) {
@@ -204,9 +246,10 @@ __device__ void scan_units_and_experts(int* unit_hist, int units, int local_expe
 }
 
 __global__ void align_scan_kernel(int* unit_hist, int units, int local_experts, int* counts,
-                                  int* mtile_prefix, int pad) {
+                                  int* mtile_prefix, int pad, int with_part) {
   extern __shared__ int tiles_smem[];
-  scan_units_and_experts(unit_hist, units, local_experts, counts, mtile_prefix, tiles_smem, pad);
+  scan_units_and_experts(unit_hist, units, local_experts, counts, mtile_prefix, tiles_smem,
+                         with_part ? tiles_smem + (local_experts + 1) : nullptr, pad);
 }
 
 // Mark the padding rows of expert e with -1; `lane`/`width` are the caller's
@@ -271,7 +314,9 @@ align_fused_kernel(const int* __restrict__ topk_ids, const int* __restrict__ exp
   for (int e = threadIdx.x & 31; e < local_experts; e += 32)
     unit_hist[size_t(warp) * local_experts + e] = running[e];
   __syncthreads();
-  scan_units_and_experts(unit_hist, kFusedWarps, local_experts, counts, mtile_prefix, tiles_smem, pad);
+  // the per-warp counters are free between the two walks and serve as the scan's partial sums
+  scan_units_and_experts(unit_hist, kFusedWarps, local_experts, counts, mtile_prefix, tiles_smem,
+                         running_all, pad);
   __syncthreads();
   for (int e = warp; e < local_experts; e += kFusedWarps)
     fill_padding(counts, mtile_prefix, e, sorted_ids, row_capacity, threadIdx.x & 31, 32, pad);
@@ -334,8 +379,10 @@ int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map
         topk_ids, expert_map, assignments, local_experts, chunk, units, scratch);
     MB200_CHECK_CUDA(cudaGetLastError());
   }
-  align_scan_kernel<<<1, 1024, size_t(local_experts + 1) * sizeof(int), stream>>>(
-      scratch, units, local_experts, sched.counts, sched.mtile_prefix, pad);
+  const size_t part_smem = size_t(local_experts + 1 + 32 * local_experts) * sizeof(int);
+  const int with_part = part_smem <= 48 * 1024;
+  align_scan_kernel<<<1, 1024, with_part ? part_smem : size_t(local_experts + 1) * sizeof(int), stream>>>(
+      scratch, units, local_experts, sched.counts, sched.mtile_prefix, pad, with_part);
   MB200_CHECK_CUDA(cudaGetLastError());
   const int sblocks = blocks > 0 ? blocks : 1;
   align_scatter_kernel<<<sblocks, kAlignThreads, hist_smem, stream>>>(

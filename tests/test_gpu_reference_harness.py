@@ -59,3 +59,28 @@ def test_reference_run_sweep_times_and_verifies_the_plugin(precision):
         assert r["timing"] == "graph", r
         assert r["verify"] == "ok", r
         assert r["latency_us"] > 0 and r["tflops"] > 0 and r["local_assignments"] == r["num_tokens"] * 8
+
+
+@pytest.mark.parametrize("precision,mode", [("fp8", "ep"), ("bf16", "ep"), ("bf16", "tp")])
+def test_reference_run_distributed_times_and_verifies_the_scheme(precision, mode, tmp_path):
+    """Two GPUs: the reference spawns its own workers, builds each rank's problem with
+    its own generator, times ``scheme.run`` with its own loop and checks every rank's
+    output against its full-model ground truth (distributed.py:36-84)."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    staged = _staged_parent()
+    if staged is None:
+        pytest.skip("reference package not staged (oracle/stage_reference.py)")
+    out = tmp_path / "rows.json"
+    env = dict(os.environ, TORCHDYNAMO_DISABLE="1", LOCALHOST="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    child = os.path.join(ROOT, "tests", "reference_distributed_child.py")
+    res = subprocess.run([sys.executable, child, ROOT, staged, precision, mode, "2", str(out)],
+                         capture_output=True, text=True, timeout=1500, env=env)
+    assert res.returncode == 0, (res.stdout[-1500:], res.stderr[-3000:])
+    payload = json.load(open(out))
+    rows = payload["results"]
+    assert [r["num_tokens"] for r in rows] == [128, 1024]
+    for r in rows:
+        assert r["verify"] == "ok" and r["latency_us"] > 0, r
