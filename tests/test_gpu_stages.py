@@ -39,6 +39,9 @@ ALIGN_CASES = [
     ("uniform", 1024, 256, 8, 8),   # EP: rank 3 of 8 owns 32 experts
     ("single", 512, 256, 8, 8),     # EP with no local assignment at all on rank 3
     ("uniform", 5000, 1024, 4, 0),  # maximum supported expert count
+    ("uniform", 65536, 256, 8, 8),  # EP=8 at 8192 tokens per rank: 524 288 assignments, 1024 units, 32 local experts
+    ("uniform", 40000, 320, 8, 0),  # a wide expert count whose unit scan still runs warp-parallel
+    ("uniform", 40000, 384, 8, 0),  # and the first that takes the one-thread-per-expert scan
 ]
 
 
