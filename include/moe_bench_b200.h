@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define MB200_ABI_VERSION 4
+#define MB200_ABI_VERSION 5
 #define MB200_PRECISION_BF16 0
 #define MB200_PRECISION_FP8 1
 #define MB200_PRECISION_FP16 2 /* the bf16 data flow with IEEE half operands and outputs */
@@ -170,7 +170,9 @@ int mb200_forward_layout(int precision, int64_t tokens, int hidden, int intermed
  * wait ran out; 150 + peer: a cross-GPU barrier did); while it is non-zero the
  * outputs are not to be trusted - read it with mb200_read_status at a point
  * where the host synchronises anyway.  Word 1 is the limit of one in-kernel
- * wait in milliseconds (0 = 4 s). */
+ * wait in milliseconds (0 = 4 s); word 2 is the limit of one cross-GPU barrier
+ * in milliseconds (0 = 3 s) - raise it where ranks may reach a barrier further
+ * apart than that (a first call that still loads modules, a stalled host). */
 int mb200_moe_forward_bf16(const void* hidden_states, const void* w1, const void* w2,
                            const int32_t* topk_ids, const float* topk_weights,
                            const int32_t* expert_map, void* out, int64_t tokens, int hidden,
@@ -266,7 +268,10 @@ int mb200_dist_forward(int precision, int expert_parallel, const void* hidden_st
                        int64_t symmetric_bytes, uint32_t seq_base, void* workspace, int64_t workspace_bytes,
                        int device, void* stream);
 /* The all-rank barrier used inside mb200_dist_forward, exposed for set-up and
- * tear-down (protocol of sm120_common.cuh:47-64, with a time limit). */
+ * tear-down (protocol of sm120_common.cuh:47-64, with a time limit).  status:
+ * null, or the head of a status block in device memory, four int32 zeroed by
+ * the caller: [0] receives 150 + peer when that peer did not arrive in time,
+ * [2] is the limit in milliseconds (0 = 3 s); [1] and [3] are not used here. */
 int mb200_peer_barrier(void* const* symmetric_ptrs, int rank, int world, uint32_t seq, int32_t* status,
                        void* stream);
 

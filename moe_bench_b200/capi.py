@@ -16,7 +16,7 @@ import torch
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libmoe_bench_b200.so")
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 PRECISION_BF16 = 0
 PRECISION_FP8 = 1
 PRECISION_FP16 = 2
@@ -374,6 +374,10 @@ def peer_pointer_array(ptrs):
 
 
 def peer_barrier(ptr_array, rank: int, world: int, seq: int, status: Optional[torch.Tensor], device) -> None:
+    if status is not None:
+        _need(status, torch.int32, "status")
+        if status.numel() < 4:
+            raise MB200Error("status: need the four-word head of a status block")
     _check(load().mb200_peer_barrier(ptr_array, rank, world, seq, _ptr(status), _stream(device)), "peer_barrier")
 
 

@@ -33,6 +33,9 @@ namespace mb200 {
 
 namespace {
 
+// Default limit of the all-rank barrier; word 2 of the status block (milliseconds, 0 = default)
+// overrides it, for hosts whose ranks may reach a barrier further apart (a first call that
+// still loads modules, a stalled host thread).
 constexpr uint64_t kBarrierLimitNs = 3ull * 1000 * 1000 * 1000;
 constexpr int kGatherLoads = 7;  // 16-byte loads a lane of the row gather keeps in flight
 
@@ -44,6 +47,8 @@ __global__ void peer_barrier_kernel(PeerTable flags, int rank, int world, uint32
   uint32_t* remote = reinterpret_cast<uint32_t*>(flags.ptr[peer]) + rank;
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
   const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.ptr[rank]) + peer;
+  const int limit_ms = status ? status[2] : 0;
+  const uint64_t limit_ns = limit_ms > 0 ? uint64_t(limit_ms) * 1000000ull : kBarrierLimitNs;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
@@ -51,7 +56,7 @@ __global__ void peer_barrier_kernel(PeerTable flags, int rank, int world, uint32
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if (int32_t(v - seq) >= 0) break;  // monotonic, wrap-safe
     if ((++spins & 0xFF) == 0) {
-      if (global_timer_ns() - t0 > kBarrierLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         if (status) atomicCAS(status, 0, kDevWaitTimeout + 50 + peer);
         break;
       }

@@ -35,7 +35,7 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 
 
 def test_abi_version_and_pure_host_queries(lib):
-    assert lib.mb200_abi_version() == capi.ABI_VERSION == 4
+    assert lib.mb200_abi_version() == capi.ABI_VERSION == 5
     # 8 assignments can hit at most 8 experts: 8 + 8*127 rows, rounded to 128
     assert lib.mb200_row_capacity(1, 8, 256, 128) == 1024
     assert lib.mb200_row_capacity(1, 8, 256, 16) == 128

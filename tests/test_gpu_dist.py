@@ -135,9 +135,10 @@ def test_scheme_world2(mode, precision, tokens, dist_name):
 def test_barrier_with_absent_peer_gives_up_with_a_status_and_the_context_stays_usable():
     """Failure detection without a fault: two local buffers stand in for the flag
     areas of two ranks and only rank 0 calls the barrier, so the flag it polls is
-    never set.  The kernel gives up after its 3 s limit, reports 150 + the missing
-    peer in the status word and returns; the late "rank" then completes the same
-    barrier at once, and the layer still runs in this context."""
+    never set.  The kernel gives up after its 3 s limit (or the limit in word 2 of
+    the status block), reports 150 + the missing peer in the status word and returns;
+    the late "rank" then completes the same barrier at once, and the layer still runs
+    in this context."""
     import time
 
     from moe_bench_b200 import capi
@@ -146,14 +147,23 @@ def test_barrier_with_absent_peer_gives_up_with_a_status_and_the_context_stays_u
     dev = torch.device("cuda", 0)
     bufs = [torch.zeros(1024, dtype=torch.int32, device=dev) for _ in range(2)]
     ptrs = capi.peer_pointer_array([b.data_ptr() for b in bufs])
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+    status[2] = 400                            # a caller-chosen barrier limit: 0.4 s
+    torch.cuda.synchronize()
+    t0 = time.time()
+    capi.peer_barrier(ptrs, 0, 2, 1, status, dev)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 0.3 < waited < 2.5, waited
+    assert int(status[0]) == 151               # 100 (a wait ran out) + 50 (barrier) + peer 1
+    status.zero_()                             # default limit: 3 s
     torch.cuda.synchronize()
     t0 = time.time()
     capi.peer_barrier(ptrs, 0, 2, 1, status, dev)
     torch.cuda.synchronize()
     waited = time.time() - t0
     assert 2.5 < waited < 20, waited
-    assert int(status.item()) == 151           # 100 (a wait ran out) + 50 (barrier) + peer 1
+    assert int(status[0]) == 151
     assert int(bufs[0][0]) == 1 and int(bufs[1][0]) == 1   # rank 0 had announced itself to both
     # the missing rank arrives late: its barrier and a repeat of rank 0's complete immediately
     status.zero_()
@@ -161,7 +171,7 @@ def test_barrier_with_absent_peer_gives_up_with_a_status_and_the_context_stays_u
     capi.peer_barrier(ptrs, 1, 2, 1, status, dev)
     capi.peer_barrier(ptrs, 0, 2, 1, status, dev)
     torch.cuda.synchronize()
-    assert time.time() - t0 < 1.0 and int(status.item()) == 0
+    assert time.time() - t0 < 1.0 and int(status[0]) == 0
     # the context is intact
     cfg = _cfg("ep", "bf16", 1)
     prob = _to_dev(P.make_problem(cfg, 50, 0), "cuda:0")
