@@ -47,6 +47,8 @@ class B200FusedExperts(MoEImplementation):
     # fp8 activation scale format: None = what the reference does on this box (asked of vLLM
     # in setup()), or "fp32" / "ue8m0" to fix it
     fp8_scale_format = None
+    # limit of one in-kernel wait in milliseconds (0 = the library's default of 4 s)
+    wait_limit_ms = 0
 
     def __init__(self) -> None:
         self._key = None
@@ -99,7 +101,8 @@ class B200FusedExperts(MoEImplementation):
         raw = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
         shift = (-raw.data_ptr()) % 1024
         self._workspace = raw[shift : shift + nbytes]
-        self._workspace[:256].zero_()  # status word
+        self._workspace[:256].zero_()  # status block: [0] first failure code, [1] wait limit in ms
+        self._workspace[:256].view(torch.int32)[1] = int(self.wait_limit_ms)
         self._out = torch.empty(t, hidden, dtype=self._dtype, device=dev)
         self._key = self._shape_key(problem)
 

@@ -154,6 +154,10 @@ class B200Scheme(DistributedScheme):
     # fp8 activation scale format: None = what the reference does on this box (asked of vLLM
     # in setup()), or "fp32" / "ue8m0" to fix it
     fp8_scale_format = None
+    # limits in milliseconds of one in-kernel wait and of one cross-GPU barrier (0 = the
+    # library's defaults of 4 s and 3 s); raise the second where ranks can be further apart
+    wait_limit_ms = 0
+    barrier_limit_ms = 0
 
     def __init__(self) -> None:
         self._buf = None
@@ -196,7 +200,9 @@ class B200Scheme(DistributedScheme):
         raw = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
         shift = (-raw.data_ptr()) % 1024
         self._workspace = raw[shift : shift + nbytes]
-        self._workspace[:256].zero_()
+        self._workspace[:256].zero_()  # status block: [0] failure code, [1] wait limit, [2] barrier limit (ms)
+        head = self._workspace[:256].view(torch.int32)
+        head[1], head[2] = int(self.wait_limit_ms), int(self.barrier_limit_ms)
         self._out = torch.empty(t, hidden, dtype=self._dtype, device=dev)
         self._hidden = problem.hidden_states.contiguous()
         self._ids = problem.topk_ids.contiguous()

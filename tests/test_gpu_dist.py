@@ -50,7 +50,9 @@ def test_scheme_world1(mode, precision, tokens):
     prob = P.make_problem(cfg, tokens, 0)
     ctx = DistContext(rank=0, world_size=1, local_rank=0, device=torch.device("cuda", 0))
     scheme = get_scheme("b200")
+    scheme.wait_limit_ms, scheme.barrier_limit_ms = 2000, 1500   # caller-chosen limits travel in the status block
     scheme.setup(_to_dev(prob, "cuda:0"), ctx)
+    assert scheme._workspace[:12].view(torch.int32).tolist() == [0, 2000, 1500]
     out = scheme.run().clone()
     for _ in range(3):  # barrier sequence numbers keep growing across calls
         again = scheme.run()
