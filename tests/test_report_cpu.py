@@ -33,6 +33,18 @@ def test_table_renders(tmp_path, capsys):
     assert json.load(open(out))["results"][0]["verify"] == "ok"
 
 
+def test_measured_line_carries_its_sweep_points():
+    """The fixture is a whole default line: its secondary list is the bf16 and fp8 token sweep."""
+    line = json.load(open(SAMPLE))
+    rows = R.rows_from_secondary(line)
+    assert sorted({(r["precision"], r["num_tokens"]) for r in rows}) == sorted(
+        (p, t) for p in ("bf16", "fp8") for t in (1, 8, 128, 2048, 8192))
+    assert all(r["verify"] == "ok" and r["latency_us"] > 0 for r in rows)
+    fp8 = {r["num_tokens"]: r["latency_us"] for r in rows if r["precision"] == "fp8"}
+    bf16 = {r["num_tokens"]: r["latency_us"] for r in rows if r["precision"] == "bf16"}
+    assert all(fp8[t] < bf16[t] for t in fp8)          # fp8 is the faster precision at every point
+
+
 def test_secondary_legs_become_rows():
     line = json.load(open(SAMPLE))
     line["secondary"] = [
