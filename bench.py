@@ -1054,7 +1054,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         # kernels of this library launched per step (memsets and copies are not kernels); derived
         # from the call sequence of the entry points, checked against the committed ncu launch list
         total_assignments = assignments * world
-        n_align = 3 if total_assignments > 16384 else 1
+        n_align = 3 if total_assignments > 8192 else 1
         if world == 1:      # align, [fp8: quantise + row gather], gate/up GEMM (16-bit: gather fused), down GEMM, combine
             kernels_per_step = n_align + 3 + (2 if fp8 else 0)
         else:

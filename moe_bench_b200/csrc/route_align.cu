@@ -96,7 +96,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int tokens, 
 constexpr int kAlignWarps = 8;
 constexpr int kAlignThreads = kAlignWarps * 32;
 constexpr int kMaxUnits = 1024;
-constexpr int kFusedMaxAssignments = 16384;
+constexpr int kFusedMaxAssignments = 8192;  // beyond this the three-kernel form is faster (about 35 us flat)
 constexpr int kFusedWarps = 32;
 
 __host__ __device__ inline int64_t unit_chunk(int64_t assignments, int units_cap) {
@@ -159,66 +159,61 @@ __global__ void align_count_kernel(const int* __restrict__ topk_ids, const int* 
 }
 
 // One block.  unit_hist[u][e] becomes the exclusive prefix over units; counts and
-// the cumulative M-tile table are written.  With `part` ([warps][E] ints of shared
-// memory) every warp scans a contiguous range of units, lanes across experts, in
-// two passes (range sums, then the prefix from the sums of the warps before it);
-// without it one thread per expert walks all units.
+// the cumulative M-tile table are written.  The block's threads form up to 32 groups
+// of E threads (thread = one expert, consecutive threads = consecutive experts, so
+// every load is a coalesced row segment); each group scans a contiguous range of
+// units in two passes: range sums into `part` ([groups][E] ints of shared memory,
+// at most blockDim.x), then the prefix starting from the sums of the groups before it.
+constexpr int kScanMaxGroups = 32;
+
 __device__ void scan_units_and_experts(int* unit_hist, int units, int local_experts, int* counts,
                                        int* mtile_prefix, int* smem_tiles /*[E+1]*/, int* part, int pad) {
-  if (part != nullptr) {
-    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per_warp = (units + warps - 1) / warps;
-    const int u_lo = warp * per_warp < units ? warp * per_warp : units;
-    const int u_hi = u_lo + per_warp < units ? u_lo + per_warp : units;
-    for (int e = lane; e < local_experts; e += 32) {
-      int sum = 0;
-      for (int u0 = u_lo; u0 < u_hi; u0 += 8) {
-        int v[8];
+  const int E = local_experts;
+  int groups = E < int(blockDim.x) ? int(blockDim.x) / E : 1;
+  if (groups > kScanMaxGroups) groups = kScanMaxGroups;
+  const int per_group = (units + groups - 1) / groups;
+  for (int e0 = 0; e0 < E; e0 += blockDim.x) {  // one trip unless E exceeds the block
+    const int g = groups > 1 ? int(threadIdx.x) / E : 0;
+    const int e = e0 + (groups > 1 ? int(threadIdx.x) % E : int(threadIdx.x));
+    const bool active = e < E && g < groups;
+    const int u_lo = g * per_group < units ? g * per_group : units;
+    const int u_hi = u_lo + per_group < units ? u_lo + per_group : units;
+    int run = 0;
+    if (groups > 1) {
+      if (active) {
+        int sum = 0;
+        for (int u0 = u_lo; u0 < u_hi; u0 += 8) {
+          int v[8];  // loads first, so eight of them are in flight together
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          v[i] = (u0 + i < u_hi) ? unit_hist[size_t(u0 + i) * local_experts + e] : 0;
+          for (int i = 0; i < 8; ++i)
+            v[i] = (u0 + i < u_hi) ? unit_hist[size_t(u0 + i) * E + e] : 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sum += v[i];
+          for (int i = 0; i < 8; ++i) sum += v[i];
+        }
+        part[g * E + e] = sum;
       }
-      part[warp * local_experts + e] = sum;
+      __syncthreads();
+      if (active)
+        for (int w = 0; w < g; ++w) run += part[w * E + e];
     }
-    __syncthreads();
-    for (int e = lane; e < local_experts; e += 32) {
-      int run = 0;
-      for (int w = 0; w < warp; ++w) run += part[w * local_experts + e];
+    if (active) {
       for (int u0 = u_lo; u0 < u_hi; u0 += 8) {
         int v[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          v[i] = (u0 + i < u_hi) ? unit_hist[size_t(u0 + i) * local_experts + e] : 0;
+          v[i] = (u0 + i < u_hi) ? unit_hist[size_t(u0 + i) * E + e] : 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          if (u0 + i < u_hi) unit_hist[size_t(u0 + i) * local_experts + e] = run;
+          if (u0 + i < u_hi) unit_hist[size_t(u0 + i) * E + e] = run;
           run += v[i];
         }
       }
-      if (warp == warps - 1) {  // the last warp's running sum is the expert's total
+      if (g == groups - 1) {  // the last group's running sum is the expert's total
         counts[e] = run;
         smem_tiles[e] = (run + pad - 1) / pad;
       }
     }
-  } else {
-    for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
-      int run = 0;
-      for (int u0 = 0; u0 < units; u0 += 8) {
-        int v[8];  // loads first, so eight of them are in flight together
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          v[i] = (u0 + i < units) ? unit_hist[size_t(u0 + i) * local_experts + e] : 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (u0 + i < units) unit_hist[size_t(u0 + i) * local_experts + e] = run;
-          run += v[i];
-        }
-      }
-      counts[e] = run;
-      smem_tiles[e] = (run + pad - 1) / pad;
-    }
+    if (groups > 1) __syncthreads();  // `part` is reused by the next trip
   }
   __syncthreads();
   if (threadIdx.x < 32) {
@@ -246,10 +241,10 @@ __device__ void scan_units_and_experts(int* unit_hist, int units, int local_expe
 }
 
 __global__ void align_scan_kernel(int* unit_hist, int units, int local_experts, int* counts,
-                                  int* mtile_prefix, int pad, int with_part) {
-  extern __shared__ int tiles_smem[];
+                                  int* mtile_prefix, int pad) {
+  extern __shared__ int tiles_smem[];  // [E+1] tiles per expert, then [blockDim.x] partial sums
   scan_units_and_experts(unit_hist, units, local_experts, counts, mtile_prefix, tiles_smem,
-                         with_part ? tiles_smem + (local_experts + 1) : nullptr, pad);
+                         tiles_smem + (local_experts + 1), pad);
 }
 
 // Mark the padding rows of expert e with -1; `lane`/`width` are the caller's
@@ -379,10 +374,8 @@ int launch_align(const int* topk_ids, int64_t assignments, const int* expert_map
         topk_ids, expert_map, assignments, local_experts, chunk, units, scratch);
     MB200_CHECK_CUDA(cudaGetLastError());
   }
-  const size_t part_smem = size_t(local_experts + 1 + 32 * local_experts) * sizeof(int);
-  const int with_part = part_smem <= 48 * 1024;
-  align_scan_kernel<<<1, 1024, with_part ? part_smem : size_t(local_experts + 1) * sizeof(int), stream>>>(
-      scratch, units, local_experts, sched.counts, sched.mtile_prefix, pad, with_part);
+  align_scan_kernel<<<1, 1024, size_t(local_experts + 1 + 1024) * sizeof(int), stream>>>(
+      scratch, units, local_experts, sched.counts, sched.mtile_prefix, pad);
   MB200_CHECK_CUDA(cudaGetLastError());
   const int sblocks = blocks > 0 ? blocks : 1;
   align_scatter_kernel<<<sblocks, kAlignThreads, hist_smem, stream>>>(

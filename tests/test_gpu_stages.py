@@ -32,16 +32,17 @@ ALIGN_CASES = [
     ("uniform", 8, 256, 8, 0),
     ("uniform", 128, 256, 8, 0),
     ("single", 300, 256, 8, 0),     # every token on experts 0..7
-    ("skewed", 2048, 256, 8, 0),    # 16384 assignments: last size of the one-block path
-    ("uniform", 2049, 256, 8, 0),   # first size of the three-kernel path, ragged tail
+    ("skewed", 1024, 256, 8, 0),    # 8192 assignments: last size of the one-block path
+    ("uniform", 1025, 256, 8, 0),   # first size of the three-kernel path, ragged tail
+    ("skewed", 2048, 256, 8, 0),
     ("uniform", 8192, 256, 8, 0),   # full-size sweep point
     ("balanced", 777, 64, 8, 0),
     ("uniform", 1024, 256, 8, 8),   # EP: rank 3 of 8 owns 32 experts
     ("single", 512, 256, 8, 8),     # EP with no local assignment at all on rank 3
     ("uniform", 5000, 1024, 4, 0),  # maximum supported expert count
     ("uniform", 65536, 256, 8, 8),  # EP=8 at 8192 tokens per rank: 524 288 assignments, 1024 units, 32 local experts
-    ("uniform", 40000, 320, 8, 0),  # a wide expert count whose unit scan still runs warp-parallel
-    ("uniform", 40000, 384, 8, 0),  # and the first that takes the one-thread-per-expert scan
+    ("uniform", 40000, 320, 8, 0),  # 320 experts: three groups of threads scan the units side by side, 64 threads idle
+    ("uniform", 40000, 384, 8, 0),  # 384 experts: two groups
 ]
 
 
