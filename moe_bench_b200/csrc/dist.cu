@@ -4,17 +4,23 @@
 // ReduceScatter dataflow of the reference's serial scheme (schemes.py:117-143).
 //
 // Every rank owns a "symmetric" buffer of identical layout that all peers have
-// mapped (flags | routing | token payload | partial outputs).  One forward:
-//   1. stage: own routing and tokens into the symmetric buffer (EP/TP fp8:
-//      quantised to e4m3 + 1x128 scales first, so fp8 travels on the wire);
+// mapped (flags | routing | token payload | partial planes | received rows).
+// One expert-parallel forward:
+//   1. stage: own routing and tokens into the symmetric buffer (fp8: quantised to
+//      e4m3 + 1x128 scales first, so fp8 travels on the wire);
 //   2. barrier;
 //   3. routing of all ranks -> ring-ordered local copy; sort-and-pad against this
-//      rank's experts; dispatch = pull the needed rows from their owners (bf16: by
-//      the dispatch warps inside the gate/up GEMM kernel, overlapped with its tiles;
-//      fp8: by a gather kernel);
-//   4. the two grouped GEMMs; the contributions of a token that landed on this
-//      rank are pre-reduced into one row of `partial`;
-//   5. barrier; the token's own rank pulls and sums the partial rows; barrier.
+//      rank's experts;
+//   4. gate/up GEMM whose helper warps pull the needed rows from their owners,
+//      granule by granule, while the tiles compute (the dispatch); down GEMM whose
+//      helper warps push every finished weighted row of another rank's token into
+//      that rank's receive buffer (the combine);
+//   5. barrier; the token's own rank sums its k received rows.
+// Tensor parallel gathers the peers' token blocks once, runs the GEMMs on its slice
+// of the intermediate dimension, sums a token's k rows and pushes the sum into the
+// owner's plane, barrier, the owner sums its W planes.  fp8 with few rows per expert
+// (tokens-on-columns kernels, no helper warps) keeps separate gather, pre-reduce
+// and pull-reduce kernels with a third barrier.
 
 #include "../../include/moe_bench_b200.h"
 #include <cstring>

@@ -1,10 +1,10 @@
-// Cross-GPU stages of the distributed layer (one process per GPU, peers'
-// buffers mapped into this process: plain 64-bit pointers over NVLink).
-//
-// Data moves by P2P *loads* issued from these kernels (a rank pulls exactly the
-// rows it needs from the owning rank's buffer); the only remote *stores* are the
-// 4-byte barrier flags.  Nothing here waits inside a compute kernel: ranks meet
-// at the barrier kernel, whose spin is bounded.
+// Cross-GPU kernels of the distributed layer that run outside the GEMMs (one
+// process per GPU, peers' buffers mapped into this process: plain 64-bit
+// pointers over NVLink).  The bulk of the traffic does not pass through this
+// file: the dispatch pulls run in helper warps of the gate/up GEMM kernels and
+// the combine pushes in helper warps of the down GEMM kernels
+// (grouped_gemm.cu, grouped_gemm_fp8.cu); the tensor-parallel sum-and-push is
+// in rows.cu.  Ranks meet at the barrier kernel, whose spin is bounded.
 //
 //   peer_barrier      every rank writes a monotonic sequence number into its slot
 //                     of every peer's flag array (st.release.sys after a system
@@ -15,17 +15,18 @@
 //   gather_routing    all ranks' topk ids / weights -> one local array in ring
 //                     order (own rank first), replacing the two small
 //                     all-gathers of schemes.py:122-127 / tk_scheme.py:682-683.
-//   dispatch gather   EP dispatch, fp8 (replaces the all-gather of schemes.py:121):
-//                     the expert rank pulls the token rows routed to its experts
-//                     straight into its sorted, padded row buffer - e4m3 rows plus
-//                     their 1x128 scales (fp8 on the wire).  The bf16 dispatch runs
-//                     inside the gate/up GEMM kernel (grouped_gemm.cu).
+//   gather_rows_fp8   EP dispatch for fp8 with few rows per expert (the
+//                     tokens-on-columns kernels have no helper warps; replaces
+//                     the all-gather of schemes.py:121): the expert rank pulls
+//                     the token rows routed to its experts straight into its
+//                     sorted, padded row buffer - e4m3 rows plus their 1x128
+//                     scales (fp8 on the wire).
 //   gather_blocks     TP: every rank's staged token block, pulled once.
-//   reduce_partials   EP combine / TP output reduce (replaces the reduce-scatter
-//                     of schemes.py:142): every expert rank has pre-reduced the
-//                     contributions of a token that landed on it into one row;
-//                     the token's own rank pulls the <= W rows that exist and sums
-//                     them in fp32 in rank order.
+//   reduce_partials   combine of that same few-rows fp8 path (replaces the
+//                     reduce-scatter of schemes.py:142): every expert rank has
+//                     pre-reduced the contributions of a token that landed on it
+//                     into one row; the token's own rank pulls the <= W rows
+//                     that exist and sums them in fp32 in rank order.
 
 #include "layer.cuh"
 
