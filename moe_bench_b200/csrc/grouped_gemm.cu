@@ -7,9 +7,10 @@
 // 32 KB of weights + at most 32 KB of tokens into shared memory for two
 // 128 x ntok x 64 products - half the bytes per MMA cycle of a 128-token tile.
 // A 128 x N x 16 tcgen05.mma takes N/2 cycles, but a K step of a tile costs about
-// 1000 cycles whatever its N between 16 and 224 (the stage pipeline, not the
-// tensor pipe, paces it), so the fewest, fullest tiles win: segments longer than
-// 256 rows are split into equal parts.
+// 1000 cycles whatever its N between 16 and 224 (the rate at which one SM takes
+// 128-byte rows from L2, about 64 B per clock, paces it, not the tensor pipe), so
+// the fewest, fullest tiles win: segments longer than 256 rows are split into
+// equal parts.
 //
 //   gate/up:  acc0 = w1[e, f0:f0+128, :] . X^T, acc1 = w1[e, N+f0 : N+f0+128, :] . X^T
 //             act[token, f0+i] = SiLU(acc0[i, token]) * acc1[i, token]      (bf16)

@@ -2,28 +2,37 @@
 //
 // Scales follow the reference's w8a8 block scheme (reference.py:65-95,119-167):
 // one fp32 scale per 128x128 weight block and one per activation row per 128
-// elements of K.  They are plain fp32 numbers (amax/448), not powers of two, so
-// the hardware block-scaled MMA cannot apply them.  Instead every 128-deep K
-// block is multiplied on the tensor cores into its own tensor-memory buffer
-// (tcgen05.mma kind::f8f6f4, 4 x K32) and the epilogue warps promote it:
+// elements of K.  The weight scales are plain fp32 numbers (amax/448), not powers
+// of two (the activation scales are either, see fp8_group_scale), so the hardware
+// block-scaled MMA cannot apply them.  Instead every 128-deep K block is multiplied
+// on the tensor cores into its own tensor-memory buffer (tcgen05.mma kind::f8f6f4,
+// 4 x K32) and the epilogue warps promote it:
 //     acc += partial * (a_scale[row, kb] * w_scale[nblock, kb])
 // in fp32 registers, in ascending K-block order like the reference.  Two
 // 256-column partial buffers let the promotion of block kb overlap the MMAs of
 // block kb+1.
 //
-// Roles per CTA (320 threads): warp 0 TMA producer (4-stage ring, one stage =
-// one K block: 128 rows x 128 B of A + 256 rows x 128 B of weights), warp 1
-// tensor-memory owner and MMA issuer, warps 2-9 epilogue.  Epilogue warp w reads
-// tensor-memory lanes 32*(w%4).. (one accumulator row per thread) and the column
-// half w/4: 128 fp32 accumulators per thread.
+// Roles per CTA (384 threads, register file re-split with setmaxnreg): warp 0 TMA
+// producer (4-stage ring, one stage = one K block: 128 rows x 128 B of A + 256 rows
+// x 128 B of weights, plus the K block's 128 activation scales as a 512-byte bulk
+// copy on the same barrier), warp 1 tensor-memory owner and MMA issuer, warps 2-3
+// helpers (gate/up: the dispatch - they pull e4m3 rows and scales of the tile's
+// tokens from their source ranks, or gather them locally, granule by granule; down,
+// expert parallel: they push finished rows to the ranks that own the tokens),
+// warps 4-11 epilogue.  Epilogue warp w reads tensor-memory lanes 32*(w%4).. (one
+// accumulator row per thread) and one column half: 128 fp32 accumulators per thread,
+// held as 64 packed pairs and updated with fma.rn.f32x2.
 //   gate/up:  columns = 64 gate + the matching 64 up outputs; at the end of the
 //             tile SiLU(gate)*up is rounded to bf16 and re-quantised per row over
 //             the tile's 128 outputs (= one quantisation group, amax exchanged
 //             between the two column halves through shared memory), so the
 //             second GEMM's A operand reaches HBM only as e4m3 + scales
-//             (reference.py:156-163).
+//             (reference.py:156-163).  Rows past the expert's last one are zeroed
+//             first (their garbage would send the divisions down the slow path).
 //   down:     columns = 128 outputs = one weight scale block; scaled by the
-//             combine weight and stored as bf16 at the row's flat assignment.
+//             combine weight, transposed through a per-warp block of shared memory
+//             and stored as bf16, 64 contiguous bytes per row, at the row's flat
+//             assignment.
 
 #include <atomic>
 
