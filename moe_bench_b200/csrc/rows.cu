@@ -3,6 +3,10 @@
 //                  out[t, :] = sum over the k local assignments of token t of
 //                  the already weighted rows y[t*k + j, :], fp32 sum, bf16 store
 //                  (reference.py:180-182).
+//   combine_push:  tensor parallel: the same sum, stored straight into the plane of
+//                  the token's owner that belongs to this rank (16-byte P2P stores);
+//   sum_planes:    the owner's sum over its W planes (the output reduce of
+//                  schemes.py:72-75,142).
 //   group_quant:   per row, per 128-wide group dynamic e4m3 quantisation of
 //                  activations (reference.py:143-145,157-163).
 // All of them move 16 bytes per thread per access and size their grids as a
